@@ -16,7 +16,9 @@ in every entry of the group. Groups may differ in how many pages a request needs
 them (`KVSpec.stride`), so every count below is per group.
 
 A group with a window gives a page back as soon as every position in it is behind
-the window of all tokens still to come; its block-table entry becomes -1. Pages that hold
+the window of all tokens still to come; its block-table entry becomes -1. So does a group
+whose queries read only their own run of positions (`KVSpec.chunk`), once the latest
+position has left a page's run behind. Pages that hold
 one of the first `keep_first` positions of such a group are kept until the request ends. All pages
 return when the request ends. Freed pages are handed out again, last freed first.
 
@@ -256,15 +258,15 @@ class CacheManager:
         return page * self.page_size + row % self.page_size
 
     def release_behind_window(self, request: RequestCache) -> int:
-        """Give back pages of windowed groups that no later token can read. With
+        """Give back pages of groups with a window or runs that no later token can read. With
         `tokens` positions written, the next query sits at position >= tokens and sees
-        keys >= tokens - window + 1. Returns how many pages were freed."""
+        keys >= tokens - window + 1, and none before the start of its own run. Returns how many
+        pages were freed."""
         freed = 0
         for g, (group, table) in enumerate(zip(self.groups, request.tables)):
-            window = group.spec.window
-            if window is None:
+            if not group.spec.forgets:
                 continue
-            dead_below = request.tokens - window + 1  # positions < this are never read again
+            dead_below = group.spec.dead_below(request.tokens)  # positions < this are never read again
             dead_rows = max(dead_below, 0) // group.spec.stride  # stored rows wholly below it
             # Pages that hold any of the first `keep_first` positions stay for the request's whole life.
             kept = -(-group.spec.stored(group.spec.keep_first) // self.page_size) if group.spec.keep_first else 0

@@ -2,6 +2,8 @@
 // width), page size and element type: the kernel of the 32-bit path, and of sizes the tiled kernels
 // refuse. A window may keep the request's first `keep_first` positions visible for good, and the
 // softmax's denominator may hold one more term exp(sink[head]) that has no key and no value.
+// With `chunk` > 0 a query sees the keys of its own run of `chunk` positions only (runs counted from
+// position 0 of the request); with `softcap` > 0 a scaled score s becomes softcap * tanh(s / softcap).
 //
 // One warp per (token, query head). Keys are visited in chunks of 32 starting at the
 // lowest visible position; in a chunk every lane scores one key (a full dot product in
@@ -23,7 +25,7 @@ __global__ void paged_attention_generic_kernel(
     T* __restrict__ out,                    // [tokens, nq * dv]
     const float* __restrict__ sink,         // [nq] or null
     int num_seqs, int max_pages, int num_pages, int nq, int nkv, int d, int dv, int page_size,
-    int window, int keep_first, float scale, int* err) {
+    int window, int keep_first, float scale, int chunk, float softcap, int* err) {
   __shared__ float qs[4][256];
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -38,7 +40,8 @@ __global__ void paged_attention_generic_kernel(
   const int seq = lo_s;
   const int pos = positions[t];
   const int kvh = head / (nq / nkv);
-  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  int first = window > 0 ? max(0, pos - window + 1) : 0;
+  if (chunk > 0) first = max(first, pos - pos % chunk);
 
   const T* qrow = q + ((size_t)t * nq + head) * d;
   for (int i = lane; i < d; i += 32) qs[warp][i] = to_f32(qrow[i]) * scale;
@@ -68,7 +71,7 @@ __global__ void paged_attention_generic_kernel(
         const T* kp = k_pages + (long long)page * page_stride + in_page * d;
         float dot = 0.f;
         for (int i = 0; i < d; ++i) dot += qs[warp][i] * to_f32(kp[i]);
-        s = dot;
+        s = softcap > 0.f ? softcap * tanhf(dot / softcap) : dot;
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -120,14 +123,16 @@ extern "C" int omnia_paged_attention_generic(
     const void* q, const void* k_pages, const void* v_pages, long long page_stride, const int* block_table,
     const int* cu_seqlens, const int* positions, const void* gate, int gate_stride, void* out, const float* sink,
     int tokens, int num_seqs, int max_pages, int num_pages, int nq, int nkv, int d, int dv, int page_size, int window,
-    int keep_first, float scale, int dtype, int* err, cudaStream_t stream) {
+    int keep_first, float scale, int chunk, float softcap, int dtype, int* err, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  if (d > 256 || dv > 256 || nkv <= 0 || nq % nkv != 0 || keep_first < 0 || (keep_first > 0 && window <= 0))
+  if (d > 256 || dv > 256 || nkv <= 0 || nq % nkv != 0 || keep_first < 0 || (keep_first > 0 && window <= 0) ||
+      chunk < 0 || softcap < 0.f || (chunk > 0 && keep_first > 0))
     return (int)cudaErrorInvalidValue;
   dim3 grid(tokens, (nq + 3) / 4);
   OMNIA_DISPATCH_DTYPE(dtype, (paged_attention_generic_kernel<T><<<grid, 128, 0, stream>>>(
                                   (const T*)q, (const T*)k_pages, (const T*)v_pages, page_stride, block_table,
                                   cu_seqlens, positions, (const T*)gate, gate_stride, (T*)out, sink, num_seqs,
-                                  max_pages, num_pages, nq, nkv, d, dv, page_size, window, keep_first, scale, err)));
+                                  max_pages, num_pages, nq, nkv, d, dv, page_size, window, keep_first, scale, chunk, softcap,
+                                  err)));
   return OMNIA_LAUNCH_RESULT();
 }

@@ -471,6 +471,9 @@ extern "C" int omnia_qk_norm_rope_store(const void* proj, int row_stride, int q_
 // the token's slot of the cache: key row (head h) at k_pages + page * page_stride + (h * page_size
 // + offset) * dk, value row at v_pages + page * page_stride + (h * page_size + offset) * dv.
 // One block per token, its warps taking the heads in turn.
+// `whole`: the norm is one root mean square over all heads of q (and one over all heads of k) with
+// weights of the whole projection's size; `interleaved`: the rotation pairs dims (2i, 2i + 1).
+#define QKV_PREPARE_MAX_NORMED 512
 template <typename T>
 __global__ void __launch_bounds__(256)
 qkv_prepare_kernel(const T* __restrict__ proj, int row_stride, int q_col, int k_col, int v_col,
@@ -479,12 +482,13 @@ qkv_prepare_kernel(const T* __restrict__ proj, int row_stride, int q_col, int k_
                    const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
                    const long long* __restrict__ slot_mapping, T* __restrict__ q_out,
                    T* __restrict__ k_pages, T* __restrict__ v_pages, long long page_stride,
-                   int page_size, long long num_slots, int* err) {
+                   int page_size, long long num_slots, int whole, int interleaved, int* err) {
   pdl_wait();
   pdl_launch_dependents();
   // One block per token: the token's angles are worked out once for all its heads.
   __shared__ float cos_s[128], sin_s[128];
   __shared__ float staged[8][256];
+  __shared__ float head_ss[QKV_PREPARE_MAX_NORMED];  // `whole`: every normed head's sum of squares
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int rhalf = inv_freq != nullptr ? rot / 2 : 0;
@@ -496,6 +500,28 @@ qkv_prepare_kernel(const T* __restrict__ proj, int row_stride, int q_col, int k_
   const long long slot = slot_mapping != nullptr ? slot_mapping[t] : -1;
   if (nkv > 0 && slot >= num_slots && threadIdx.x == 0) atomicOr(err, OMNIA_ERR_SLOT);
   float* v = staged[warp];
+  float whole_scale[2] = {1.f, 1.f};
+  if (whole && eps >= 0.f) {
+    // One root mean square over all heads of q, one over all heads of k: the heads' sums of squares
+    // first, then every thread adds them in the heads' order.
+    for (int hs = warp; hs < nq + nkv; hs += warps) {
+      const int col = hs < nq ? q_col + hs * dk : k_col + (hs - nq) * dk;
+      const T* src = proj + (size_t)t * row_stride + col;
+      float ss = 0.f;
+      for (int i = lane; i < dk; i += 32) {
+        const float a = to_f32(src[i]) + (bias ? to_f32(bias[col + i]) : 0.f);
+        ss += a * a;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) head_ss[hs] = ss;
+    }
+    __syncthreads();
+    float sq = 0.f, sk = 0.f;
+    for (int h = 0; h < nq; ++h) sq += head_ss[h];
+    for (int h = 0; h < nkv; ++h) sk += head_ss[nq + h];
+    whole_scale[0] = rsqrtf(sq / (float)(nq * dk) + eps);
+    if (nkv > 0) whole_scale[1] = rsqrtf(sk / (float)(nkv * dk) + eps);
+  }
   for (int hs = warp; hs < nq + 2 * nkv; hs += warps) {
     const int kind = hs < nq ? 0 : (hs < nq + nkv ? 1 : 2);
     const int head = kind == 0 ? hs : (kind == 1 ? hs - nq : hs - nq - nkv);
@@ -516,22 +542,25 @@ qkv_prepare_kernel(const T* __restrict__ proj, int row_stride, int q_col, int k_
       continue;
     }
     const float* w = kind == 0 ? q_weight : k_weight;
+    if (w != nullptr && whole) w += head * d;  // a weight of the projection's size, not of the head's
     float ss = 0.f;
     for (int i = lane; i < d; i += 32) {
       const float a = to_f32(src[i]) + (b ? to_f32(b[i]) : 0.f);
       v[i] = a;
       ss += a * a;
     }
-    const float scale = eps >= 0.f ? rsqrtf(warp_sum(ss) / (float)d + eps) : 1.f;
+    const float scale = eps < 0.f ? 1.f : whole ? whole_scale[kind] : rsqrtf(warp_sum(ss) / (float)d + eps);
     __syncwarp();
     if (eps >= 0.f)
       for (int i = lane; i < d; i += 32) v[i] = v[i] * scale * (w ? w[i] : 1.f);
     __syncwarp();
     for (int i = lane; i < rhalf; i += 32) {
       const float c = cos_s[i], sn = sin_s[i];
-      const float a0 = v[i], a1 = v[i + rhalf];
-      dst[i] = from_f32<T>(a0 * c - a1 * sn);
-      dst[i + rhalf] = from_f32<T>(a1 * c + a0 * sn);
+      // Which two dims turn together: (i, i + rot / 2), or neighbours (2i, 2i + 1).
+      const int i0 = interleaved ? 2 * i : i, i1 = interleaved ? 2 * i + 1 : i + rhalf;
+      const float a0 = v[i0], a1 = v[i1];
+      dst[i0] = from_f32<T>(a0 * c - a1 * sn);
+      dst[i1] = from_f32<T>(a1 * c + a0 * sn);
     }
     for (int i = 2 * rhalf + lane; i < d; i += 32) dst[i] = from_f32<T>(v[i]);
     __syncwarp();  // the staging row is read before the warp's next head overwrites it
@@ -542,16 +571,17 @@ extern "C" int omnia_qkv_prepare(const void* proj, int row_stride, int q_col, in
                                  int dk, int dv, const void* bias, const float* q_weight, const float* k_weight,
                                  float eps, const float* inv_freq, int rot, const int* positions,
                                  const long long* slot_mapping, void* q_out, void* k_pages, void* v_pages,
-                                 long long page_stride, int page_size, long long num_slots, int tokens, int dtype,
-                                 int* err, cudaStream_t stream) {
+                                 long long page_stride, int page_size, long long num_slots, int tokens, int whole,
+                                 int interleaved, int dtype, int* err, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  if (dk > 256 || dv > 256 || rot > dk || (rot & 1)) return (int)cudaErrorInvalidValue;
+  if (dk > 256 || dv > 256 || rot > dk || (rot & 1) || (whole && nq + nkv > QKV_PREPARE_MAX_NORMED))
+    return (int)cudaErrorInvalidValue;
   const int heads = nq + 2 * nkv;
   const int threads = heads >= 8 ? 256 : heads >= 4 ? 128 : 64;
   OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(qkv_prepare_kernel<T>, tokens, threads, 0, stream, (const T*)proj, row_stride, q_col,
                                           k_col, v_col, nq, nkv, dk, dv, (const T*)bias, q_weight, k_weight, eps,
                                           inv_freq, rot, positions, slot_mapping, (T*)q_out, (T*)k_pages, (T*)v_pages,
-                                          page_stride, page_size, num_slots, err)));
+                                          page_stride, page_size, num_slots, whole, interleaved, err)));
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -630,7 +660,8 @@ extern "C" int omnia_round_rows(const float* x, void* h, long long total, int dt
 
 // ---------------------------------------------------------------------------------
 // The clamped gated unit: g = min(gu[t, i], limit), u = clamp(gu[t, inner + i], -limit, limit);
-// act[t, i] = g * sigmoid(alpha * g) * (u + 1), in float32, rounded once.
+// act[t, i] = g * sigmoid(alpha * g) * (u + 1), in float32, rounded once. limit < 0 selects the unit
+// whose gate goes through a relu instead: act[t, i] = relu(gu[t, i]) * gu[t, inner + i].
 template <typename T>
 __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ act, long long total, int inner,
                                    float alpha, float limit) {
@@ -640,6 +671,10 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ act
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
     const long long t = idx / inner;
     const int i = (int)(idx - t * inner);
+    if (limit < 0.f) {  // the gate through a relu, nothing clamped: relu(gate) * up
+      act[idx] = from_f32<T>(fmaxf(to_f32(gu[t * 2 * inner + i]), 0.f) * to_f32(gu[t * 2 * inner + inner + i]));
+      continue;
+    }
     const float g = fminf(to_f32(gu[t * 2 * inner + i]), limit);
     const float u = fminf(fmaxf(to_f32(gu[t * 2 * inner + inner + i]), -limit), limit);
     act[idx] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));

@@ -284,7 +284,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // cap > 0: the clamped unit (gate below cap, up within +-cap and moved by one, slope `multiplier`).
                 const float gc = cap > 0.f ? fminf(g, cap) : g;
                 const float uc = cap > 0.f ? fminf(fmaxf(u, -cap), cap) + 1.f : u;
-                v[e] = __fdividef(gc, 1.f + __expf(-multiplier * gc)) * uc;
+                // cap < 0: the gate through a relu, relu(gate) * up.
+                v[e] = cap < 0.f ? fmaxf(g, 0.f) * u : __fdividef(gc, 1.f + __expf(-multiplier * gc)) * uc;
               }
               const int col = n0 + c + j;
               if (col + 1 < pair_offset && (pair_offset & 1) == 0) {
@@ -411,7 +412,8 @@ int launch(const void* a, const void* w, void* out, int m, int n, int k, int pai
 // The grouped form: a [m, k] sorted by expert, w [experts * n, k], tiles [max_tiles, 3] and tile_count on the device.
 template <int BLOCK_N, int STAGES, int EPI>
 int launch_grouped(const void* a, const void* w, void* out, int m, int n, int k, int experts, int pair_offset,
-                   const int* tiles, const int* tile_count, int max_tiles, int* err, cudaStream_t stream) {
+                   const int* tiles, const int* tile_count, int max_tiles, float multiplier, float cap, int* err,
+                   cudaStream_t stream) {
   CUtensorMap map_a, map_b;
   const int b_box = EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
   if (!make_map(&map_a, a, m, k, BLOCK_M) || !make_map(&map_b, w, experts * n, k, b_box)) return (int)cudaErrorInvalidValue;
@@ -430,7 +432,7 @@ int launch_grouped(const void* a, const void* w, void* out, int m, int n, int k,
   const long long total = (long long)n_tiles * max_tiles;
   const int grid = (int)(total < sm_count ? total : sm_count);
   launch_pdl(gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI>, grid, THREADS, smem, stream,
-             map_a, map_b, out, m, n, k, pair_offset, 1.f, 0.f, max_tiles, n_tiles, tiles, tile_count, n, err);
+             map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, max_tiles, n_tiles, tiles, tile_count, n, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -445,7 +447,6 @@ extern "C" int omnia_gemm_tcgen05(const void* a, const void* w, void* out, int m
   if (k <= 0 || k % 8 != 0 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
   if (epilogue == EPI_SWIGLU) {
     if (n % 2) return (int)cudaErrorInvalidValue;
-    if (cap < 0.f) return (int)cudaErrorInvalidValue;
     return launch<256, 4, EPI_SWIGLU>(a, w, out, m, n, k, n / 2, cap > 0.f ? multiplier : 1.f, cap, err, stream);
   }
   if (epilogue == EPI_SOFTCAP) return launch<256, 4, EPI_SOFTCAP>(a, w, out, m, n, k, 0, multiplier, cap, err, stream);
@@ -461,17 +462,19 @@ extern "C" int omnia_gemm_tcgen05(const void* a, const void* w, void* out, int m
 
 // The grouped product of routed experts: a [m, k] rows sorted by expert; w [experts, n, k]; tiles
 // [max_tiles, 3] = (expert, first row, rows <= 128) and tile_count [1] in device memory. epilogue 0:
-// out [m, n] = a w_e^T; 1: n = 2 * inner (gate rows, then up rows), out [m, inner] = silu(gate) * up.
+// out [m, n] = a w_e^T; 1: n = 2 * inner (gate rows, then up rows), out [m, inner] = silu(gate) * up, or with
+// cap > 0 the clamped unit (the sigmoid's slope in `multiplier`), with cap < 0 relu(gate) * up.
 extern "C" int omnia_gemm_tcgen05_grouped(const void* a, const void* w, void* out, int m, int n, int k, int experts,
                                           int epilogue, const int* tiles, const int* tile_count, int max_tiles,
-                                          int* err, cudaStream_t stream) {
+                                          float multiplier, float cap, int* err, cudaStream_t stream) {
   if (m == 0 || n == 0 || max_tiles == 0) return 0;
   if (k <= 0 || k % 8 != 0 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || experts < 1) return (int)cudaErrorInvalidValue;
   if (epilogue == EPI_SWIGLU) {
     if (n % 2) return (int)cudaErrorInvalidValue;
-    return launch_grouped<256, 4, EPI_SWIGLU>(a, w, out, m, n, k, experts, n / 2, tiles, tile_count, max_tiles, err, stream);
+    return launch_grouped<256, 4, EPI_SWIGLU>(a, w, out, m, n, k, experts, n / 2, tiles, tile_count, max_tiles,
+                                              cap > 0.f ? multiplier : 1.f, cap, err, stream);
   }
   if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
-  return launch_grouped<256, 4, EPI_STORE>(a, w, out, m, n, k, experts, 0, tiles, tile_count, max_tiles, err, stream);
+  return launch_grouped<256, 4, EPI_STORE>(a, w, out, m, n, k, experts, 0, tiles, tile_count, max_tiles, 1.f, 0.f, err, stream);
 }
 

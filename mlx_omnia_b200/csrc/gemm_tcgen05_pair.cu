@@ -320,7 +320,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 // cap > 0: the clamped unit (gate below cap, up within +-cap and moved by one, slope `multiplier`).
                 const float gc = cap > 0.f ? fminf(g, cap) : g;
                 const float uc = cap > 0.f ? fminf(fmaxf(u, -cap), cap) + 1.f : u;
-                v[e] = __fdividef(gc, 1.f + __expf(-multiplier * gc)) * uc;
+                // cap < 0: the gate through a relu, relu(gate) * up.
+                v[e] = cap < 0.f ? fmaxf(g, 0.f) * u : __fdividef(gc, 1.f + __expf(-multiplier * gc)) * uc;
               }
               const int col = n0 + c + j;
               if (col + 1 < pair_offset && (pair_offset & 1) == 0) {
@@ -568,7 +569,6 @@ extern "C" int omnia_gemm_tcgen05_pair(const void* a, const void* w, void* out, 
   if (k <= 0 || k % 8 != 0 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
   if (epilogue == EPI_SWIGLU) {
     if (n % 2) return (int)cudaErrorInvalidValue;
-    if (cap < 0.f) return (int)cudaErrorInvalidValue;
     return launch<EPI_SWIGLU>(a, w, out, m, n, k, n / 2, cap > 0.f ? multiplier : 1.f, cap, err, stream);
   }
   if (epilogue == EPI_SOFTCAP) return launch<EPI_SOFTCAP>(a, w, out, m, n, k, 0, multiplier, cap, err, stream);

@@ -434,9 +434,11 @@ gemv_stream_kernel(const bf16* __restrict__ a, const __grid_constant__ CUtensorM
           up = __bfloat162float(__float2bfloat16_rn(up));
           // cap > 0 is the clamped unit: gate held below cap, up within +-cap and moved by one, the
           // sigmoid's slope in `multiplier`; otherwise silu(gate) * up (multiplier 1).
+          // cap < 0: the gate through a relu, relu(gate) * up.
           float g = gate;
           if (cap > 0.f) g = fminf(g, cap), up = fminf(fmaxf(up, -cap), cap) + 1.f;
-          reinterpret_cast<bf16*>(out)[(size_t)token * inner + col] = __float2bfloat16_rn(g / (1.f + expf(-multiplier * g)) * up);
+          reinterpret_cast<bf16*>(out)[(size_t)token * inner + col] =
+              __float2bfloat16_rn(cap < 0.f ? fmaxf(g, 0.f) * up : g / (1.f + expf(-multiplier * g)) * up);
         } else {
           const int col = tile * TILE_ROWS + r;
           if (col >= n) continue;
@@ -542,7 +544,7 @@ int launch_rows(const bf16* a, const bf16* w, void* out, int m, int n, int k, in
 }  // namespace
 
 // epilogue: 0 store bfloat16 [m, n] (cap 1, 2, 3: relu^2, tanh-GELU or SiLU of the product; 0: as it is); 1 SwiGLU, w = [gate rows | up rows] with n = 2 * inner,
-// out bfloat16 [m, inner] (cap > 0: the clamped unit min(gate, cap) * sigmoid(multiplier * min(gate, cap)) * (clamp(up, +-cap) + 1)); 2 soft cap, out float32 [m, n]. err: the device error word.
+// out bfloat16 [m, inner] (cap > 0: the clamped unit min(gate, cap) * sigmoid(multiplier * min(gate, cap)) * (clamp(up, +-cap) + 1); cap < 0: relu(gate) * up); 2 soft cap, out float32 [m, n]. err: the device error word.
 extern "C" int omnia_gemv_stream(const void* a, const void* w, void* out, int m, int n, int k, int epilogue,
                                  float multiplier, float cap, int* err, cudaStream_t stream) {
   if (m == 0 || n == 0) return 0;
@@ -553,7 +555,6 @@ extern "C" int omnia_gemv_stream(const void* a, const void* w, void* out, int m,
   const PendingStep none{};
   if (epilogue == EPI_SWIGLU) {
     if (n % 2) return (int)cudaErrorInvalidValue;
-    if (cap < 0.f) return (int)cudaErrorInvalidValue;
     return launch_rows<EPI_SWIGLU, false>(ap, wp, out, m, n, k, n / 2, cap > 0.f ? multiplier : 1.f, cap, none, err, stream);
   }
   if (epilogue == EPI_SOFTCAP)

@@ -1,0 +1,170 @@
+// Linear attention with one constant decay per head ("lightning attention"), as a recurrence over a
+// request's tokens from a state that is carried in a slot:
+//
+//   q_t = silu(projected q), k_t = silu(projected k)   [heads, DK]
+//   v_t = silu(projected v)                            [heads, dv]
+//   S_t = decay_h * S_(t-1) + k_t v_t^T                [DK, dv] per head, float32
+//   o_t = S_t^T q_t                                    (no other scale)
+//
+// followed by one RMS norm over a token's heads side by side with a weight of that size, and a
+// sigmoid gate:  out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate).
+//
+// The recurrence kernel is sequential in a request's tokens and parallel over (request, head, run
+// of value columns): the columns of S are independent. A column is held by P threads, each with
+// DK / P of its rows in registers; between tokens there are only shuffles inside a warp. The
+// activations are taken in float32 and rounded to the element type, as a product with the
+// activation in its epilogue would store them; the state, the decay and every sum stay float32.
+// It serves decode steps (one token a request) and prompts' portions of any length alike; the
+// order of a column's additions does not depend on how a prompt was cut.
+//
+// Compiled per key width: -DLIGHTNING_DK=<DK>.
+#include "common.cuh"
+
+#ifndef LIGHTNING_DK
+#define LIGHTNING_DK 64
+#endif
+#define LIGHTNING_CHUNK 16  // tokens staged in shared memory at a time
+
+namespace {
+
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.f + expf(-x)); }
+
+template <typename T, int P>
+__global__ void __launch_bounds__(1024) lightning_recurrence_kernel(
+    const T* __restrict__ proj, int stride, int q_col, int k_col, int v_col, int H, int dv, int cols, int parts,
+    const float* __restrict__ decay, float* __restrict__ S_state, const int* __restrict__ cu_seqlens,
+    const int* __restrict__ state_slots, float* __restrict__ o_raw) {
+  pdl_wait();
+  pdl_launch_dependents();
+  constexpr int DK = LIGHTNING_DK;
+  constexpr int R = (DK + P - 1) / P;
+  constexpr int SEG = R + 1;     // a thread's rows, padded so that the P segments fall on different banks
+  constexpr int VROW = P * SEG;  // floats of one token's vector of DK
+  constexpr int TC = LIGHTNING_CHUNK;
+  extern __shared__ float shared[];
+  float* qs = shared;            // [TC][VROW]
+  float* ks = qs + TC * VROW;    // [TC][VROW]
+  float* vs = ks + TC * VROW;    // [TC][cols]
+  const int head = blockIdx.x / parts, part = blockIdx.x % parts, seq = blockIdx.y;
+  const int col0 = part * cols;
+  const int begin = cu_seqlens[seq], end = cu_seqlens[seq + 1];
+  if (end <= begin) return;
+  const int slot = state_slots[seq];
+  const int j = threadIdx.x / P, p = threadIdx.x % P;
+  const bool live = j < cols && col0 + j < dv;
+  const float lambda = decay[head];
+
+  float S[R];
+  float* mine = S_state + (((size_t)slot * H + head) * DK) * dv + col0 + j;
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int r = p * R + i;
+    S[i] = (live && r < DK) ? mine[(size_t)r * dv] : 0.f;
+  }
+
+  for (int t0 = begin; t0 < end; t0 += TC) {
+    const int n = min(TC, end - t0);
+    __syncthreads();  // the chunk before has been read
+    for (int idx = threadIdx.x; idx < n * DK; idx += blockDim.x) {
+      const int tok = idx / DK, i = idx % DK;
+      const T* src = proj + (size_t)(t0 + tok) * stride + head * DK + i;
+      const int at = tok * VROW + (i / R) * SEG + i % R;
+      qs[at] = to_f32(from_f32<T>(silu_f32(to_f32(src[q_col]))));
+      ks[at] = to_f32(from_f32<T>(silu_f32(to_f32(src[k_col]))));
+    }
+    for (int idx = threadIdx.x; idx < n * cols; idx += blockDim.x) {
+      const int tok = idx / cols, c = idx % cols;
+      vs[idx] = col0 + c < dv
+                    ? to_f32(from_f32<T>(silu_f32(to_f32(proj[(size_t)(t0 + tok) * stride + v_col + head * dv + col0 + c]))))
+                    : 0.f;
+    }
+    __syncthreads();
+    for (int tok = 0; tok < n; ++tok) {
+      const float* kt = ks + tok * VROW + p * SEG;
+      const float* qt = qs + tok * VROW + p * SEG;
+      const float v = live ? vs[tok * cols + j] : 0.f;
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+        if (p * R + i < DK) {
+          S[i] = lambda * S[i] + kt[i] * v;
+          o += S[i] * qt[i];
+        }
+#pragma unroll
+      for (int w = 1; w < P; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+      if (live && p == 0) o_raw[(size_t)(t0 + tok) * H * dv + head * dv + col0 + j] = o;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int r = p * R + i;
+    if (live && r < DK) mine[(size_t)r * dv] = S[i];
+  }
+}
+
+// out[t] = o[t] / sqrt(mean(o[t]^2) + eps) * w * sigmoid(gate[t]) over a token's whole row of
+// `width` = heads * dv; a block per token.
+template <typename T>
+__global__ void lightning_out_kernel(const float* __restrict__ o_raw, const T* __restrict__ gate_rows, int gate_stride,
+                                     const float* __restrict__ norm_w, float eps, int width, T* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ float red[33];
+  const size_t t = blockIdx.x;
+  const float* o = o_raw + t * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) ss += o[c] * o[c];
+  const float r = rsqrtf(block_sum(ss, red) / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float gate = to_f32(gate_rows[t * gate_stride + c]);
+    out[t * width + c] = from_f32<T>(o[c] * r * norm_w[c] / (1.f + expf(-gate)));
+  }
+}
+
+}  // namespace
+
+extern "C" int omnia_lightning_dk(void) { return LIGHTNING_DK; }
+
+// proj: the projected rows [tokens, stride] with q at q_col, k at k_col (heads * DK each) and v at
+// v_col (heads * dv); decay float32 [heads]; S_state float32 [slots, heads, DK, dv], updated in place;
+// o_raw float32 [tokens, heads * dv] receives the unnormed outputs. parts: runs of columns a head is
+// cut into (dv must divide into them).
+extern "C" int omnia_lightning_recurrence(const void* proj, int stride, int q_col, int k_col, int v_col, int H, int dv,
+                                          int parts, const float* decay, float* S_state, const int* cu_seqlens,
+                                          const int* state_slots, int num_seqs, float* o_raw, int dtype,
+                                          cudaStream_t stream) {
+  if (num_seqs == 0) return 0;
+  if (H < 1 || dv < 1 || parts < 1 || dv % parts != 0) return (int)cudaErrorInvalidValue;
+  const int cols = dv / parts;
+  const dim3 grid(H * parts, num_seqs);
+#define OMNIA_LIGHTNING_LAUNCH(P)                                                                              \
+  do {                                                                                                         \
+    constexpr int R = (LIGHTNING_DK + P - 1) / P;                                                              \
+    const size_t smem = sizeof(float) * ((size_t)2 * LIGHTNING_CHUNK * P * (R + 1) + LIGHTNING_CHUNK * cols);  \
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(lightning_recurrence_kernel<T, P>,                            \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      return (int)cudaGetLastError();                                                                          \
+    launch_pdl(lightning_recurrence_kernel<T, P>, grid, dim3((cols * P + 31) / 32 * 32), smem, stream,         \
+               (const T*)proj, stride, q_col, k_col, v_col, H, dv, cols, parts, decay, S_state, cu_seqlens,    \
+               state_slots, o_raw);                                                                            \
+  } while (0)
+  OMNIA_DISPATCH_DTYPE(dtype, {
+    if (cols * 4 <= 1024 && LIGHTNING_DK >= 16) OMNIA_LIGHTNING_LAUNCH(4);
+    else if (cols * 2 <= 1024 && LIGHTNING_DK >= 8) OMNIA_LIGHTNING_LAUNCH(2);
+    else if (cols <= 1024) OMNIA_LIGHTNING_LAUNCH(1);
+    else return (int)cudaErrorInvalidValue;
+  });
+#undef OMNIA_LIGHTNING_LAUNCH
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// out [tokens, width] = o_raw normed over the whole row (weight norm_w [width], eps) times
+// sigmoid(gate_rows[t, :width]) (rows gate_stride apart).
+extern "C" int omnia_lightning_out(const float* o_raw, const void* gate_rows, int gate_stride, const float* norm_w,
+                                   float eps, int width, int tokens, void* out, int dtype, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(lightning_out_kernel<T>, dim3(tokens), dim3(threads), 0, stream, o_raw,
+                                          (const T*)gate_rows, gate_stride, norm_w, eps, width, (T*)out)));
+  return OMNIA_LAUNCH_RESULT();
+}

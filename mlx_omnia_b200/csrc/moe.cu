@@ -23,6 +23,16 @@ namespace {
 
 constexpr int TILE_ROWS = 64;  // rows of a tile of the grouped products
 
+// What an expert does with its gate and up values: silu(gate) * up, or with limit > 0 the clamped
+// unit g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(alpha * g) * (u + 1).
+__device__ __forceinline__ float gated_unit(float gate, float up, float alpha, float limit) {
+  if (limit > 0.f) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+  }
+  return gate / (1.f + expf(-gate)) * up;
+}
+
 // ---------------------------------------------------------------------------------
 // A block routes TOK consecutive tokens (8 where there are many: every router row is then fetched
 // once for eight tokens instead of once a token; 1 in a small step, which wants warps, not reuse).
@@ -224,7 +234,7 @@ template <typename T, bool DUAL>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const T* __restrict__ a, const int* __restrict__ source, const T* __restrict__ w,
                    T* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ tile_count,
-                   int n, int k) {
+                   int n, int k, float alpha, float limit) {
   pdl_wait();
   pdl_launch_dependents();
   if ((int)blockIdx.x >= *tile_count) return;
@@ -284,7 +294,7 @@ moe_product_kernel(const T* __restrict__ a, const int* __restrict__ source, cons
       const int c = n0 + tx * 4 + j;
       if (c >= n) continue;
       float v = acc[0][i][j];
-      if (DUAL) v = v / (1.f + expf(-v)) * acc[1][i][j];
+      if (DUAL) v = gated_unit(v, acc[1][i][j], alpha, limit);
       out[(size_t)(row0 + r) * n + c] = from_f32<T>(v);
     }
   }
@@ -325,7 +335,7 @@ template <bool DUAL>
 __global__ void __launch_bounds__(128)
 moe_product_tc_kernel(const bf16* __restrict__ a, const int* __restrict__ source, const bf16* __restrict__ w,
                       bf16* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ tile_count,
-                      int n, int k) {
+                      int n, int k, float alpha, float limit) {
   pdl_wait();
   pdl_launch_dependents();
   if ((int)blockIdx.x >= *tile_count) return;
@@ -428,7 +438,7 @@ moe_product_tc_kernel(const bf16* __restrict__ a, const int* __restrict__ source
         const int c = n0 + 8 * j + 2 * t4 + e;
         if (c >= n) continue;
         float v = acc[0][j][2 * half + e];
-        if (DUAL) v = v / (1.f + expf(-v)) * acc[PARTS - 1][j][2 * half + e];
+        if (DUAL) v = gated_unit(v, acc[PARTS - 1][j][2 * half + e], alpha, limit);
         out[(size_t)(row0 + r) * n + c] = __float2bfloat16_rn(v);
       }
     }
@@ -490,6 +500,37 @@ extern "C" int omnia_moe_route(const void* h, const float* router, const float* 
   return (int)cudaErrorInvalidValue;
 }
 
+// Routing without a router: row `ids[t]` of an integer table [vocab, top] names token t's experts
+// (the entries of a row differ), each with the weight 1 / top. An entry outside the experts, or a
+// token id outside the table, sets the error word's token bit and the row falls to expert 0.
+__global__ void moe_route_table_kernel(const int* __restrict__ ids, const int* __restrict__ table, int tokens, int vocab,
+                                       int experts, int top, int* __restrict__ choice, float* __restrict__ weight,
+                                       int* __restrict__ counts, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= tokens * top) return;
+  const int id = ids[i / top];
+  int e = id >= 0 && id < vocab ? table[(size_t)id * top + i % top] : -1;
+  if (e < 0 || e >= experts) {
+    atomicOr(err, OMNIA_ERR_TOKEN_ID);
+    e = 0;
+  }
+  choice[i] = e;
+  weight[i] = 1.f / (float)top;
+  atomicAdd(counts + e, 1);
+}
+
+extern "C" int omnia_moe_route_table(const int* ids, const int* table, int tokens, int vocab, int experts, int top,
+                                     int* choice, float* weight, int* counts, int* err, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (top < 1 || experts < 1 || vocab < 1) return (int)cudaErrorInvalidValue;
+  const int pairs = tokens * top;
+  launch_pdl(moe_route_table_kernel, (pairs + 255) / 256, 256, 0, stream, ids, table, tokens, vocab, experts, top, choice,
+             weight, counts, err);
+  return OMNIA_LAUNCH_RESULT();
+}
+
 extern "C" int omnia_moe_tile_rows() { return TILE_ROWS; }
 
 // After `route`: the sorted order (offsets, place, source) and the list of row tiles (of at most `tile_rows`
@@ -513,9 +554,11 @@ extern "C" int omnia_moe_plan(const int* choice, int* counts, int* cursors, int*
 }
 
 // dual != 0: w holds [experts, 2 n, k] (gate rows, then up rows) and out = silu(gate) * up.
+// limit > 0: the clamped unit instead, g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + 1).
 extern "C" int omnia_moe_product(const void* a, const int* source, const void* w, void* out, const int* tiles,
-                                 const int* tile_count, int max_tiles, int n, int k, int dual, int dtype,
-                                 int tensor_cores, cudaStream_t stream) {
+                                 const int* tile_count, int max_tiles, int n, int k, int dual, float alpha,
+                                 float limit, int dtype, int tensor_cores, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   const dim3 grid(max_tiles, (n + 63) / 64);
   if (tensor_cores) {
@@ -532,19 +575,19 @@ extern "C" int omnia_moe_product(const void* a, const int* source, const void* w
     }
     if (dual)
       launch_pdl(moe_product_tc_kernel<true>, grid, 128, tc_smem_bytes(true), stream, (const bf16*)a, source,
-                 (const bf16*)w, (bf16*)out, tiles, tile_count, n, k);
+                 (const bf16*)w, (bf16*)out, tiles, tile_count, n, k, alpha, limit);
     else
       launch_pdl(moe_product_tc_kernel<false>, grid, 128, tc_smem_bytes(false), stream, (const bf16*)a, source,
-                 (const bf16*)w, (bf16*)out, tiles, tile_count, n, k);
+                 (const bf16*)w, (bf16*)out, tiles, tile_count, n, k, alpha, limit);
     return OMNIA_LAUNCH_RESULT();
   }
   OMNIA_DISPATCH_DTYPE(dtype, {
     if (dual)
       launch_pdl(moe_product_kernel<T, true>, grid, 256, 0, stream, (const T*)a, source, (const T*)w, (T*)out, tiles,
-                 tile_count, n, k);
+                 tile_count, n, k, alpha, limit);
     else
       launch_pdl(moe_product_kernel<T, false>, grid, 256, 0, stream, (const T*)a, source, (const T*)w, (T*)out, tiles,
-                 tile_count, n, k);
+                 tile_count, n, k, alpha, limit);
   });
   return OMNIA_LAUNCH_RESULT();
 }

@@ -133,5 +133,5 @@ class Engine:
         `stored`, vectors float32), without going through a folder."""
         architecture = resolve_architecture(raw_config)
         tensors = architecture.random_tensors(architecture.parse(raw_config), seed)
-        tensors = {k: (t if t.dim() < 2 else t.to(stored)) for k, t in tensors.items()}
+        tensors = {k: (t if t.dim() < 2 or not t.is_floating_point() else t.to(stored)) for k, t in tensors.items()}
         return cls.from_tensors(raw_config, tensors, args)

@@ -226,10 +226,14 @@ def kv_layout(kv: KVView) -> tuple[int, int, int, int, int, int]:
 
 def qkv_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, nq: int, dk: int, bias: torch.Tensor | None,
                 q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float | None,
-                inv_freq: torch.Tensor | None, positions: torch.Tensor, kv: KVView, store: bool) -> torch.Tensor:
+                inv_freq: torch.Tensor | None, positions: torch.Tensor, kv: KVView, store: bool,
+                whole: bool = False, interleaved: bool = False) -> torch.Tensor:
     """Per head of the projected rows: bias (the whole row's, [columns]), RMS norm with a weight of the
     head's size (q and k), rotation of the first 2 * len(inv_freq) dims in half-split pairs; q out as
-    [tokens, nq, dk], and with `store` the keys and the values (of a width of their own) into the cache."""
+    [tokens, nq, dk], and with `store` the keys and the values (of a width of their own) into the cache.
+    `whole`: the norm is one root mean square over all heads of q at once (and one over all heads of k),
+    its weights of the whole projection's size ([nq * dk], [nkv * dk]); `interleaved`: the rotation pairs
+    dims (2i, 2i + 1) instead of (i, i + half)."""
     tokens, stride = proj.shape
     k_ptr, v_ptr, page_stride, nkv, kdim, dv = kv_layout(kv)
     if kdim != dk:
@@ -239,11 +243,12 @@ def qkv_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, nq: int,
     fn = _function("elementwise", "omnia_qkv_prepare",
                    [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                     c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
-                    c_longlong, c_int, c_int, c_void_p, c_void_p])
+                    c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(_ptr(proj), stride, q_col, k_col, v_col, nq, nkv if store else 0, dk, dv, _ptr(bias), _ptr(q_weight),
               _ptr(k_weight), -1.0 if eps is None else eps, _ptr(inv_freq), rot, _ptr(positions),
               _ptr(kv.slot_mapping) if store else None, _ptr(q), k_ptr, v_ptr, page_stride, kv.page_size,
-              kv.pages.shape[0] * kv.page_size, tokens, _code(proj.dtype), _ptr(error_word(proj.device)), _stream()),
+              kv.pages.shape[0] * kv.page_size, tokens, int(whole), int(interleaved), _code(proj.dtype),
+              _ptr(error_word(proj.device)), _stream()),
            "qkv_prepare")
     return q
 
@@ -590,7 +595,8 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
                     gate: torch.Tensor | None = None, gate_col: int = 0,
                     projection: Projection | None = None, wide: bool | None = None,
                     sink: torch.Tensor | None = None, window: int | None = -1,
-                    keep_first: int | None = None) -> torch.Tensor:
+                    keep_first: int | None = None, chunk: int | None = None,
+                    softcap: float | None = None) -> torch.Tensor:
     """Causal (windowed) attention of this step's queries over the paged cache, the
     output multiplied by sigmoid(gate) when `gate` (the projected rows; the gate's
     columns start at `gate_col`) is given.  -> [tokens, nq * dv]
@@ -602,6 +608,10 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
     mma.sync kernels and by the tcgen05 prefill kernel that runs two blocks to an SM (every block is
     then listed whole), not by the one that gives a block its SM; values of another width than the
     keys run on the generic kernel.
+
+    `chunk` n: a query sees only the keys of its own run of n positions (runs counted from the request's
+    position 0, wherever a prompt was cut); `softcap` c: a scaled score s becomes c tanh(s / c) ahead of
+    the softmax. Both are taken by the generic kernel and by the mma.sync kernels.
 
     With `projection` (only where `decode_fusable` holds) q is not given: the kernel makes the
     queries and the new keys and values from the projected rows, and writes the latter to the cache.
@@ -626,17 +636,20 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
     gate_stride = 0 if gate is None else gate.shape[1]
     err = _ptr(error_word(q.device))
     max_pages, num_pages = kv.block_table.shape[1], kv.pages.shape[0]
-    if dv != d or not tiled_attention_supported(q.dtype, nq, nkv, d):
+    chunk, softcap = int(chunk or 0), float(softcap or 0.0)
+    if chunk and keep:
+        raise KernelError("a mask of runs keeps no first positions")
+    if dv != d or not tiled_attention_supported(q.dtype, nq, nkv, d) or chunk or softcap:
         if projection is not None:
             raise KernelError("the generic attention kernel takes queries, not projected rows")
         fn = _function("attention_generic", "omnia_paged_attention_generic",
                        [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                        c_int, c_float, c_int, c_void_p, c_void_p])
+                        c_int, c_float, c_int, c_float, c_int, c_void_p, c_void_p])
         _check(fn(_ptr(q), k_ptr, v_ptr, page_stride, _ptr(kv.block_table), _ptr(step.cu_seqlens),
                   _ptr(step.positions), gate_ptr, gate_stride, _ptr(out), _ptr(sink), tokens, step.num_seqs, max_pages,
-                  num_pages, nq, nkv, d, dv, kv.page_size, kv.window or 0, keep, scale, _code(q.dtype), err,
-                  _stream()), "paged_attention")
+                  num_pages, nq, nkv, d, dv, kv.page_size, kv.window or 0, keep, scale, chunk, softcap,
+                  _code(q.dtype), err, _stream()), "paged_attention")
         return out
     defines = {"HEAD_DIM": d, "GROUP": nq // nkv}
     # Requests that bring a single token take the split-key decode kernel, in a decode-only step
@@ -1019,6 +1032,26 @@ def linear_clamped_glu(a: torch.Tensor, gate_up: torch.Tensor, alpha: float, lim
     return clamped_glu(_library_mm(a, gate_up), alpha, limit)
 
 
+def linear_relu_glu(a, gate_up: torch.Tensor) -> torch.Tensor:
+    """relu(a @ gate^T) * (a @ up^T) with gate_up = [gate rows | up rows] -> [rows, inner]. The unit sits
+    where SwiGLU does (the gated epilogues' third form, selected by a negative limit): the
+    weight-streaming kernel up to 16 rows, the tcgen05 kernels from FUSED_GATE_ROWS on; in between,
+    and on the 32-bit path, the library's product and the unit's own kernel. `a` may be a PendingStep."""
+    a = settle(a)
+    if _skinny(a, gate_up):
+        out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
+        return _gemv_stream(a, gate_up, out, 1, 1.0, -1.0)
+    if _tensor_core(a, gate_up, FUSED_GATE_ROWS):
+        out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
+        return _gemm_tcgen05(a, gate_up, out, 1, 1.0, -1.0)
+    gu = _library_mm(a, gate_up)
+    rows, inner = gu.shape[0], gu.shape[1] // 2
+    act = torch.empty(rows, inner, dtype=gu.dtype, device=gu.device)
+    fn = _function("elementwise", "omnia_clamped_glu", [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p])
+    _check(fn(_ptr(gu), _ptr(act), rows, inner, 1.0, -1.0, _code(gu.dtype), _stream()), "relu_glu")
+    return act
+
+
 def linear_softcap(a: torch.Tensor, weight: torch.Tensor, multiplier: float, cap: float | None) -> torch.Tensor:
     """float32 logits = cap * tanh((a @ weight^T) * multiplier / cap) -> [rows, n]."""
     if _skinny(a, weight):
@@ -1217,6 +1250,53 @@ def delta_rule(conv: torch.Tensor, channels: int, groups: int, heads: int, dk: i
 
 
 # ------------------------------------------------------------------------------------
+# Linear attention with a constant decay per head (csrc/lightning.cu)
+
+
+def lightning_parts(requests: int, heads: int, dv: int, sms: int) -> int:
+    """Into how many runs of columns the recurrence kernel cuts a head's value channels: the fewest
+    equal runs (of at least 8 columns) that give every SM a block, 1 when (request, head) pairs
+    alone do."""
+    blocks = requests * heads
+    best = 1
+    for parts in range(1, dv + 1):
+        if dv % parts or dv // parts < 8:
+            continue
+        best = parts
+        if blocks * parts >= sms:
+            break
+    return best if blocks < sms else 1
+
+
+def lightning_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gate_col: int, heads: int, dk: int,
+                        dv: int, decay: torch.Tensor, norm_weight: torch.Tensor, eps: float, S: torch.Tensor,
+                        step: StepContext, parts: int | None = None) -> torch.Tensor:
+    """Linear attention over this step's tokens, request by request from the state in `S`
+    [slots, heads, dk, dv] (float32, updated in place): q, k, v = silu of the projected rows' columns
+    from q_col, k_col (heads * dk each) and v_col (heads * dv); per head S <- decay_h S + k v^T,
+    o = S^T q; then one RMS norm over a token's heads side by side (weight [heads * dv], `eps`) and the
+    gate sigmoid(columns from gate_col). -> [tokens, heads * dv]"""
+    tokens, stride = proj.shape
+    width = heads * dv
+    if parts is None:
+        parts = lightning_parts(step.num_seqs, heads, dv, sm_count(proj.device))
+    o_raw = torch.empty(tokens, width, dtype=torch.float32, device=proj.device)
+    out = torch.empty(tokens, width, dtype=proj.dtype, device=proj.device)
+    fn = _function("lightning", "omnia_lightning_recurrence",
+                   [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                    c_int, c_void_p, c_int, c_void_p], {"LIGHTNING_DK": dk})
+    _check(fn(_ptr(proj), stride, q_col, k_col, v_col, heads, dv, parts, _ptr(decay), _ptr(S), _ptr(step.cu_seqlens),
+              _ptr(step.state_slots), step.num_seqs, _ptr(o_raw), _code(proj.dtype), _stream()), "lightning_recurrence")
+    fn = _function("lightning", "omnia_lightning_out",
+                   [c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_void_p],
+                   {"LIGHTNING_DK": dk})
+    gate = proj.data_ptr() + gate_col * proj.element_size()
+    _check(fn(_ptr(o_raw), gate, stride, _ptr(norm_weight), eps, width, tokens, _ptr(out), _code(proj.dtype), _stream()),
+           "lightning_out")
+    return out
+
+
+# ------------------------------------------------------------------------------------
 # Attention over a latent cache (csrc/attention_latent.cu)
 
 LATENT_MAX_RANK = 512
@@ -1343,6 +1423,21 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | 
     return choice, weight
 
 
+def moe_route_table(token_ids: torch.Tensor, table: torch.Tensor, experts: int,
+                    counts: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Routing by a table instead of a router: row `token_ids[t]` of `table` (int32 [vocab, top]) names
+    token t's experts, each with the weight 1 / top; -> (choice int32 [rows, top], weight float32
+    [rows, top]), the choices counted into `counts` (int32 [experts], zero before the call)."""
+    rows, (vocab, top) = token_ids.shape[0], table.shape
+    choice = torch.empty(rows, top, dtype=torch.int32, device=table.device)
+    weight = torch.empty(rows, top, dtype=torch.float32, device=table.device)
+    fn = _function("moe", "omnia_moe_route_table",
+                   [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(token_ids), _ptr(table), rows, vocab, experts, top, _ptr(choice), _ptr(weight), _ptr(counts),
+              _ptr(error_word(table.device)), _stream()), "moe_route_table")
+    return choice, weight
+
+
 MOE_TILE_ROWS = 64
 """Rows of a tile of the grouped products of csrc/moe.cu (the tcgen05 kernel's grouped form takes 128)."""
 
@@ -1352,9 +1447,11 @@ grouped products run on the tcgen05 kernel (tiles of 128 rows of one expert each
 would leave most of every tile empty); below, on the mma.sync kernel with tiles of 64 rows."""
 
 
-def moe_experts(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, gate_up: torch.Tensor,
+def moe_experts(h: torch.Tensor, router: torch.Tensor | None, correction: torch.Tensor | None, gate_up: torch.Tensor,
                 down: torch.Tensor, top: int, step: StepContext | None = None,
-                tensor_cores: bool | None = None, tcgen05: bool | None = None) -> torch.Tensor:
+                tensor_cores: bool | None = None, tcgen05: bool | None = None,
+                table: torch.Tensor | None = None, token_ids: torch.Tensor | None = None,
+                alpha: float = 1.0, limit: float = 0.0) -> torch.Tensor:
     """A routed mixture of gated feed-forward experts over the rows of `h` [rows, hidden]:
     y = sum over a row's `top` choices of score * expert(h), expert e being
     down[e] (silu(gate_e h) * (up_e h)) with gate_up [experts, 2 inner, hidden] (gate rows, then up
@@ -1362,7 +1459,11 @@ def moe_experts(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor 
     identity experts (their output is h). Nothing is asked of the host: rows are sorted by expert on
     the device, and the grouped products walk a tile list made there. bfloat16 runs on the tensor
     cores: the tcgen05 kernel's grouped form for many rows (`tcgen05` names the choice), mma.sync for
-    few (`tensor_cores` False keeps both off); float32 on the ordinary cores."""
+    few (`tensor_cores` False keeps both off); float32 on the ordinary cores.
+
+    With `table` (int32 [vocab, top]) and the rows' `token_ids` there is no router: a token's experts are
+    its id's row of the table, each weighing 1 / top. `limit` > 0 makes every expert the clamped unit
+    g = min(gate h, limit), u = clamp(up h, -limit, limit), down(g sigmoid(alpha g) (u + 1))."""
     rows, hidden = h.shape
     experts, inner = gate_up.shape[0], gate_up.shape[1] // 2
     pairs = rows * top
@@ -1377,7 +1478,10 @@ def moe_experts(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor 
     max_tiles = min(pairs, -(-pairs // tile_rows) + experts)
     counts, cursors = _step_buffers(step, device, {"moe_counts": (experts, torch.int32, True),
                                                    "moe_cursors": (experts, torch.int32, True)})
-    choice, weight = moe_route(h, router, correction, experts, top, counts)
+    if table is not None:
+        choice, weight = moe_route_table(token_ids[:rows], table, experts, counts)
+    else:
+        choice, weight = moe_route(h, router, correction, experts, top, counts)
     ints = torch.empty(2 * pairs + experts + 1 + 3 * max_tiles + 1, dtype=torch.int32, device=device)
     place, source = ints[:pairs], ints[pairs: 2 * pairs]
     offsets = ints[2 * pairs: 2 * pairs + experts + 1]
@@ -1397,20 +1501,20 @@ def moe_experts(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor 
                   _stream()), "moe_gather")
         grouped = _function("gemm_tcgen05", "omnia_gemm_tcgen05_grouped",
                             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
-                             c_void_p, c_void_p])
+                             c_float, c_float, c_void_p, c_void_p])
         err = _ptr(error_word(device))
         _check(grouped(_ptr(sorted_rows), _ptr(gate_up), _ptr(act), pairs, 2 * inner, hidden, experts, 1, _ptr(tiles),
-                       _ptr(tile_count), max_tiles, err, _stream()), "gemm_tcgen05_grouped")
+                       _ptr(tile_count), max_tiles, alpha, limit, err, _stream()), "gemm_tcgen05_grouped")
         _check(grouped(_ptr(act), _ptr(down), _ptr(out), pairs, hidden, inner, experts, 0, _ptr(tiles),
-                       _ptr(tile_count), max_tiles, err, _stream()), "gemm_tcgen05_grouped")
+                       _ptr(tile_count), max_tiles, 1.0, 0.0, err, _stream()), "gemm_tcgen05_grouped")
     else:
         product = _function("moe", "omnia_moe_product",
-                            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_void_p])
+                            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_float, c_float, c_int, c_int, c_void_p])
         _check(product(_ptr(h), _ptr(source), _ptr(gate_up), _ptr(act), _ptr(tiles), _ptr(tile_count), max_tiles, inner,
-                       hidden, 1, _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
+                       hidden, 1, alpha, limit, _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
         _check(product(_ptr(act), None, _ptr(down), _ptr(out), _ptr(tiles), _ptr(tile_count), max_tiles, hidden, inner, 0,
-                       _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
+                       1.0, 0.0, _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
     y = torch.empty_like(h)
     fn = _function("moe", "omnia_moe_combine",
                    [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])

@@ -214,6 +214,15 @@ class SinkWindowAttention(Mixer):
                 unscaled, with no key and no value
     own_kv:     False for a layer without k/v tensors that reads another layer's cache (as that cache
                 holds the keys: normed and rotated) with queries, window and sink of its own
+    norm_over:  "head": the norm above, every head by itself; "projection": one root mean square over
+                all of a token's query heads at once (and one over all its key heads), the weights
+                `q.norm` [heads * dim] and `k.norm` [kv_heads * dim] of the whole projection's size
+    gated:      the heads' outputs are multiplied element by element by sigmoid(g h) (`g`
+                [heads * vdim, hidden]) ahead of the output projection; g reads the mixer's own input
+    chunk:      None, or the length of the runs that positions are cut into (from the request's
+                position 0): a query sees key j <= i only of its own run
+    softcap:    None, or c: a scaled score s becomes c tanh(s / c) ahead of the softmax
+    The position part may pair dims half-split (i, i + dims / 2) or interleaved (2i, 2i + 1).
 
     Tensors: `q` [heads * dim, hidden], `k` [kv_heads * dim, hidden], `v` [kv_heads * vdim, hidden],
     `o` [hidden, heads * vdim]."""
@@ -223,49 +232,64 @@ class SinkWindowAttention(Mixer):
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
                  window: int | None = None, keep_first: int = 0, norm_eps: float | None = None,
-                 position: PartSpec | None = None, bias: bool = False, sink: bool = False, own_kv: bool = True) -> None:
+                 position: PartSpec | None = None, bias: bool = False, sink: bool = False, own_kv: bool = True,
+                 norm_over: str = "head", gated: bool = False, chunk: int | None = None,
+                 softcap: float | None = None) -> None:
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads do not divide into {kv_heads} groups")
         if dim > 256 or vdim > 256:
             raise ValueError(f"head widths of at most 256, got {dim} and {vdim}")
         if keep_first and window is None:
             keep_first = 0  # everything is visible anyway
+        if norm_over not in ("head", "projection"):
+            raise ValueError(f"norm_over is 'head' or 'projection', not {norm_over!r}")
+        if chunk is not None and (chunk < 1 or keep_first):
+            raise ValueError("chunk is a positive number of positions, and keeps no first positions")
+        if softcap is not None and softcap <= 0:
+            raise ValueError(f"softcap must be positive, got {softcap}")
         self.hidden, self.heads, self.kv_heads, self.dim, self.vdim = hidden, heads, kv_heads, dim, vdim
         self.scale, self.window, self.keep_first, self.norm_eps = float(scale), window, int(keep_first), norm_eps
         self.bias, self.sink, self.own_kv = bias, sink, own_kv
+        self.norm_over, self.gated, self.chunk, self.softcap = norm_over, gated, chunk, softcap
         self.position = POSITIONS.build(position or PartSpec("none"))
-        if getattr(self.position, "pairing", "half") != "half":
-            raise ValueError("sink_window_attention rotates half-split pairs")
+        self.interleaved = getattr(self.position, "pairing", "half") == "interleaved"
         if getattr(self.position, "dims", 0) > dim:
             raise ValueError(f"{self.position.dims} rotary dims do not fit a head of {dim}")
 
     def kv_spec(self) -> KVSpec:
-        return KVSpec(((self.kv_heads, self.dim), (self.kv_heads, self.vdim)), self.window, keep_first=self.keep_first)
+        return KVSpec(((self.kv_heads, self.dim), (self.kv_heads, self.vdim)), self.window, keep_first=self.keep_first,
+                      chunk=self.chunk)
 
     def tensors(self) -> dict[str, TensorSpec]:
         H, G, dk, dv = self.heads, self.kv_heads, self.dim, self.vdim
         specs = {"q": TensorSpec((H * dk, self.hidden)), "o": TensorSpec((self.hidden, H * dv))}
         if self.bias:
             specs["q.b"] = TensorSpec((H * dk,))
+        whole = self.norm_over == "projection"
         if self.norm_eps is not None:
-            specs["q.norm"] = TensorSpec((dk,), "vector")
+            specs["q.norm"] = TensorSpec((H * dk if whole else dk,), "vector")
         if self.sink:
             specs["sink"] = TensorSpec((H,), "vector")
+        if self.gated:
+            specs["g"] = TensorSpec((H * dv, self.hidden))
         if self.own_kv:
             specs["k"], specs["v"] = TensorSpec((G * dk, self.hidden)), TensorSpec((G * dv, self.hidden))
             if self.bias:
                 specs["k.b"], specs["v.b"] = TensorSpec((G * dk,)), TensorSpec((G * dv,))
             if self.norm_eps is not None:
-                specs["k.norm"] = TensorSpec((dk,), "vector")
+                specs["k.norm"] = TensorSpec((G * dk if whole else dk,), "vector")
         return specs
 
     def load(self, tensors, runtime) -> None:
         super().load(tensors, runtime)
         self.position.load({}, runtime)
         names = ["q", "k", "v"] if self.own_kv else ["q"]
+        if self.gated:
+            names.append("g")  # last, so that the columns of q, k and v stay where they are without it
         rows = [tensors[name] for name in names]
         self.k_col = self.heads * self.dim
         self.v_col = self.k_col + self.kv_heads * self.dim
+        self.gate_col = (self.v_col + self.kv_heads * self.vdim) if self.own_kv else self.k_col
         total = sum(r.shape[0] for r in rows)
         pad = -total % 8  # rows of the operand in steps of 8, for the kernels that want them so
         if pad:
@@ -273,7 +297,8 @@ class SinkWindowAttention(Mixer):
         self.in_proj = torch.cat(rows, dim=0).contiguous()
         self.in_bias = None
         if self.bias:
-            parts = [tensors[name + ".b"] for name in names]
+            parts = [tensors[name + ".b"] if name != "g" else torch.zeros(tensors["g"].shape[0], dtype=rows[0].dtype,
+                                                                          device=rows[0].device) for name in names]
             if pad:
                 parts.append(torch.zeros(pad, dtype=parts[0].dtype, device=parts[0].device))
             self.in_bias = torch.cat(parts).contiguous()
@@ -290,7 +315,8 @@ class SinkWindowAttention(Mixer):
         proj = ops.linear(h, self.in_proj)
         q = ops.qkv_prepare(proj, 0, self.k_col, self.v_col, self.heads, self.dim, self.in_bias, self.q_norm,
                             self.k_norm, self.norm_eps, self.position.table(), ctx.step.positions, ctx.kv,
-                            store=self.own_kv)
-        out = ops.paged_attention(q, ctx.kv, ctx.step, self.scale, sink=self.sink_logits, window=self.window,
-                                  keep_first=self.keep_first)
+                            store=self.own_kv, whole=self.norm_over == "projection", interleaved=self.interleaved)
+        out = ops.paged_attention(q, ctx.kv, ctx.step, self.scale, gate=proj if self.gated else None,
+                                  gate_col=self.gate_col, sink=self.sink_logits, window=self.window,
+                                  keep_first=self.keep_first, chunk=self.chunk, softcap=self.softcap)
         return ops.linear(out, self.o)

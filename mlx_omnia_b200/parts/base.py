@@ -67,12 +67,16 @@ class KVSpec:
              (their pages are never given back); 0 without a window.
     stride:  positions per stored row (1: one row for every position; n: one row for every
              n positions, as a mixer that keeps a compressed history would want).
+    chunk:   None, or the length of the runs that positions are cut into, counted from a request's
+             position 0, when a query reads only the keys of its own run: everything before the run
+             of the latest position can never be read again.
     Layers with equal specs share one group of pages."""
 
     rows: tuple[tuple[int, int], ...]
     window: int | None = None
     stride: int = 1
     keep_first: int = 0
+    chunk: int | None = None
 
     def __post_init__(self) -> None:
         if not self.rows or any(h < 1 or w < 1 for h, w in self.rows):
@@ -81,6 +85,24 @@ class KVSpec:
             raise ValueError("stride and window must be at least 1")
         if self.keep_first < 0 or (self.keep_first and self.window is None):
             raise ValueError("keep_first is a number of positions (at least 0) kept beside a window")
+        if self.chunk is not None and (self.chunk < 1 or self.keep_first):
+            raise ValueError("chunk is a positive number of positions, and keeps no first positions")
+
+    def dead_below(self, tokens: int) -> int:
+        """With `tokens` positions written, positions below this can never be read again: the next
+        query sits at position >= tokens, sees keys >= tokens - window + 1 and none before the start
+        of its own run."""
+        dead = 0
+        if self.window is not None:
+            dead = max(dead, tokens - self.window + 1)
+        if self.chunk is not None:
+            dead = max(dead, tokens - tokens % self.chunk)
+        return dead
+
+    @property
+    def forgets(self) -> bool:
+        """Whether old positions ever become unreadable (a window or runs)."""
+        return self.window is not None or self.chunk is not None
 
     @classmethod
     def keys_and_values(cls, kv_heads: int, head_dim: int, window: int | None = None) -> "KVSpec":
@@ -282,6 +304,11 @@ class KVView:
     def keep_first(self) -> int:
         """How many first positions stay readable beside the window."""
         return self.spec.keep_first if self.spec is not None else 0
+
+    @property
+    def chunk(self) -> int | None:
+        """The length of the runs the group forgets by (None: it keeps no such runs)."""
+        return self.spec.chunk if self.spec is not None else None
 
     def row(self, index: int) -> torch.Tensor:
         """Row `index` of every page: [num_pages, heads, page_size, width]."""

@@ -99,6 +99,67 @@ class SandwichBlock(_TwoBranchBlock):
         return x, residual_step(x, m, n["post_feedforward_layernorm"], exit_norm, ctx.exit_may_pend)
 
 
+@register_block("scaled_sandwich")
+class ScaledSandwichBlock(Block):
+    """A norm before and after each branch, the normed branch multiplied by a constant on its way
+    into the residual: x += m * after(mixer(before(x))), then x += m * after2(ff(before2(x))). The
+    feed-forward may be missing (the block then has one branch and two norms).
+
+    mixer:        PartSpec of the mixer; feed_forward: PartSpec or None
+    norms:        {"norm1", "norm1b"} and, with a feed-forward, {"norm2", "norm2b"}: the norm before
+                  and the norm after (b) each branch
+    branch_scale: m. It is folded into the after-norms' weights when they are loaded (one float32
+                  product a weight), so the fused residual step needs no factor of its own; an
+                  after-norm must therefore carry a weight.
+    """
+
+    def __init__(self, mixer: PartSpec, feed_forward: PartSpec | None, norms: dict[str, PartSpec],
+                 branch_scale: float = 1.0, mixer_name: str = "mix", feed_forward_name: str = "mlp") -> None:
+        self.mixer = MIXERS.build(mixer)
+        self.feed_forward = FEED_FORWARDS.build(feed_forward) if feed_forward is not None else None
+        wanted = ("norm1", "norm1b", "norm2", "norm2b") if feed_forward is not None else ("norm1", "norm1b")
+        if set(wanted) - set(norms):
+            raise ValueError(f"scaled_sandwich needs the norms {wanted}")
+        self.norms = {name: NORMS.build(norms[name]) for name in wanted}
+        self.branch_scale = float(branch_scale)
+        self.mixer_name, self.feed_forward_name = mixer_name, feed_forward_name
+        self.entry_norm = self.norms["norm1"]
+
+    def children(self):
+        yield self.mixer_name, self.mixer
+        if self.feed_forward is not None:
+            yield self.feed_forward_name, self.feed_forward
+        yield from self.norms.items()
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {f"{name}.{local}": spec for name, part in self.children() for local, spec in part.tensors().items()}
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        for name, part in self.children():
+            prefix = name + "."
+            part.load({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, runtime)
+        for name in ("norm1b", "norm2b"):
+            norm = self.norms.get(name)
+            if norm is None:
+                continue
+            if not isinstance(norm, RMSNorm) or norm.weight is None or norm.groups != 1:
+                raise ValueError(f"scaled_sandwich's {name} must be an ungrouped rms_norm with a weight")
+            if self.branch_scale != 1.0:
+                norm.weight = (norm.weight * self.branch_scale).contiguous()
+
+    def forward(self, x, h, ctx, exit_norm):
+        n = self.norms
+        a = self.mixer.forward(h if getattr(self.mixer, "takes_pending", False) else ops.settle(h), ctx)
+        x = ops.residual_after(h, x)
+        if self.feed_forward is None:
+            return x, residual_step(x, a, n["norm1b"], exit_norm, ctx.exit_may_pend)
+        h2 = residual_step(x, a, n["norm1b"], n["norm2"], getattr(self.feed_forward, "takes_pending", False))
+        m = self.feed_forward.forward(h2, ctx)
+        x = ops.residual_after(h2, x)
+        return x, residual_step(x, m, n["norm2b"], exit_norm, ctx.exit_may_pend)
+
+
 @register_block("pre_norm")
 class PreNormBlock(_TwoBranchBlock):
     """Two norms, one before each branch; branches are added as they are."""

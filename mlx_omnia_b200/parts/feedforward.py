@@ -92,6 +92,71 @@ class ClampedGLUMLP(FeedForward):
         return ops.linear(ops.linear_clamped_glu(h, self.gate_up, self.alpha, self.limit), self.down)
 
 
+@register_feed_forward("relu_glu_mlp")
+class ReluGLUMLP(FeedForward):
+    """down(relu(gate(h)) * up(h)), no biases.
+
+    hidden, inner: widths. Tensors: `gate`, `up` [inner, hidden] (stacked into one operand at load),
+    `down` [hidden, inner].
+    """
+
+    def __init__(self, hidden: int, inner: int) -> None:
+        self.hidden, self.inner = hidden, inner
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {"gate": TensorSpec((self.inner, self.hidden)), "up": TensorSpec((self.inner, self.hidden)),
+                "down": TensorSpec((self.hidden, self.inner))}
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        self.gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
+        self.down = tensors["down"].contiguous()
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        return ops.linear(ops.linear_relu_glu(h, self.gate_up), self.down)
+
+
+@register_feed_forward("table_experts")
+class TableExperts(FeedForward):
+    """A mixture of `experts` small clamped gated units of which every token uses `top`, chosen by
+    no router: row `token id` of an integer table names the token's experts (the entries of a row
+    differ), and each of them weighs 1 / top.
+
+    hidden, inner: widths of an expert; vocab: rows of the table; limit, alpha: an expert is
+    down(g sigmoid(alpha g) (u + 1)) with g = min(gate h, limit), u = clamp(up h, -limit, limit).
+    Tensors: `table` [vocab, top] (integers), and per expert i `e<i>.gate`, `e<i>.up` [inner, hidden],
+    `e<i>.down` [hidden, inner] (stacked at load).
+    """
+
+    def __init__(self, hidden: int, inner: int, experts: int, top: int, vocab: int, limit: float,
+                 alpha: float = 1.702) -> None:
+        if experts < 1 or not 1 <= top <= experts:
+            raise ValueError(f"table_experts of {experts} experts, {top} a token")
+        if limit <= 0:
+            raise ValueError(f"table_experts needs a positive limit, got {limit}")
+        self.hidden, self.inner, self.experts, self.top, self.vocab = hidden, inner, experts, top, vocab
+        self.limit, self.alpha = float(limit), float(alpha)
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        specs = {"table": TensorSpec((self.vocab, self.top), "table_i32")}
+        for e in range(self.experts):
+            specs[f"e{e}.gate"] = TensorSpec((self.inner, self.hidden))
+            specs[f"e{e}.up"] = TensorSpec((self.inner, self.hidden))
+            specs[f"e{e}.down"] = TensorSpec((self.hidden, self.inner))
+        return specs
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        self.table = tensors["table"].contiguous()
+        self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
+                                    for e in range(self.experts)]).contiguous()
+        self.down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        return ops.moe_experts(h, None, None, self.gate_up, self.down, self.top, ctx.step, table=self.table,
+                               token_ids=ctx.step.token_ids, alpha=self.alpha, limit=self.limit)
+
+
 @register_feed_forward("routed_experts")
 class RoutedExperts(FeedForward):
     """A mixture of `experts` small gated feed-forward layers of which every token uses `top`.

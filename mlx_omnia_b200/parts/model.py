@@ -111,8 +111,11 @@ class DecoderModel:
             if kv is None or owner is None or kv.rows != owner.rows or kv.stride != owner.stride:
                 raise ValueError(f"a schedule entry reads a cache of {specs[entry.reads]} but its mixer keeps {kv}")
             window = None if kv.window is None or owner.window is None else max(kv.window, owner.window)
+            chunk = owner.chunk if kv.chunk == owner.chunk else None
+            if chunk is None and (kv.chunk is None) != (owner.chunk is None):
+                window = None  # one of the two may look back without a bound that the other shares
             owned[entry.reads] = KVSpec(owner.rows, window, owner.stride,
-                                        max(kv.keep_first, owner.keep_first) if window is not None else 0)
+                                        max(kv.keep_first, owner.keep_first) if window is not None else 0, chunk)
         needs = []
         for e, entry in enumerate(schedule):
             mixer = self.blocks[entry.layer].mixer

@@ -6,6 +6,10 @@ read-out sees the token's own write). q, k and v come through a short causal con
 q and k are unit vectors per head (q also times dim^-1/2); g = exp(-exp(A_log) softplus(low-rank(h) +
 dt_bias)); beta = sigmoid(b(h)); o is RMS-normed per head, weighted, gated by sigmoid(low-rank(h)),
 and projected out.
+
+`decay_attention` is linear attention with one constant decay per head: per head S <- decay_h S +
+k v^T and o = S^T q with q, k and v behind SiLU and no other scale; the heads' outputs side by side
+are RMS-normed together, weighted, gated by sigmoid(g(h)), and projected out.
 """
 
 from __future__ import annotations
@@ -95,4 +99,54 @@ class ChannelDelta(Mixer):
                               qk, self.dim ** -0.5, decay, self.A_log, self.dt_bias, self.beta_col, self.heads)
         out = ops.delta_rule(conv, self.channels, self.kv_heads, self.heads, self.dim, self.vdim, proj, 0, gate,
                              self.norm_weight, self.norm_eps, state["S"], state["conv"], self.conv, step)
+        return ops.linear(out, self.o)
+
+
+@register_mixer("decay_attention")
+class DecayAttention(Mixer):
+    """hidden: model width; heads of `dim` (queries and keys) and `vdim` (values); decay: one constant
+    in (0, 1] per head; norm_eps: eps of the output norm.
+
+    Tensors: q, k [heads * dim, hidden]; v, g [heads * vdim, hidden]; norm [heads * vdim];
+    o [hidden, heads * vdim].
+    State (float32): S [heads, dim, vdim], zeros at a request's start."""
+
+    graph_safe = True
+    graph_safe_mixed = True
+    takes_pending = True  # h goes to the in-projection and nowhere else
+
+    def __init__(self, hidden: int, heads: int, dim: int, vdim: int, decay: tuple[float, ...], norm_eps: float) -> None:
+        decay = tuple(float(d) for d in decay)
+        if len(decay) != heads:
+            raise ValueError(f"decay_attention of {heads} heads was given {len(decay)} decays")
+        if dim < 1 or dim > 256 or vdim < 1:
+            raise ValueError(f"decay_attention takes keys of 1 to 256 and values of at least 1, got {dim} and {vdim}")
+        self.hidden, self.heads, self.dim, self.vdim, self.decay, self.norm_eps = hidden, heads, dim, vdim, decay, float(norm_eps)
+
+    def state_spec(self):
+        return StateSpec((self.heads, self.dim, self.vdim), torch.float32)
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        qk, v, d = self.heads * self.dim, self.heads * self.vdim, self.hidden
+        return {"q": TensorSpec((qk, d)), "k": TensorSpec((qk, d)), "v": TensorSpec((v, d)), "g": TensorSpec((v, d)),
+                "norm": TensorSpec((v,), "vector"), "o": TensorSpec((d, v))}
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        # One operand [q | k | v | g] (rows padded to a multiple of 8): a single input projection.
+        rows = [tensors[name] for name in ("q", "k", "v", "g")]
+        qk, v = self.heads * self.dim, self.heads * self.vdim
+        self.k_col, self.v_col, self.gate_col = qk, 2 * qk, 2 * qk + v
+        total = self.gate_col + v
+        if total % 8:
+            rows.append(torch.zeros(8 - total % 8, self.hidden, dtype=rows[0].dtype, device=rows[0].device))
+        self.in_proj = torch.cat(rows, dim=0).contiguous()
+        self.norm_weight = tensors["norm"].contiguous()
+        self.o = tensors["o"].contiguous()
+        self.decays = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(runtime.device)
+
+    def forward(self, h, ctx) -> torch.Tensor:
+        proj = ops.linear(h, self.in_proj)
+        out = ops.lightning_attention(proj, 0, self.k_col, self.v_col, self.gate_col, self.heads, self.dim, self.vdim,
+                                      self.decays, self.norm_weight, self.norm_eps, ctx.state, ctx.step)
         return ops.linear(out, self.o)

@@ -21,13 +21,13 @@ from mlx_omnia_b200.registry import resolve_architecture
 def write_random_model(folder: str | Path, config: dict[str, Any], seed: int,
                        dtype: torch.dtype = torch.bfloat16) -> Path:
     """Create `folder` with config.json and model.safetensors; tensors are drawn in
-    float32 from `seed` and stored as `dtype` (norm vectors always as float32)."""
+    float32 from `seed` and stored as `dtype` (norm vectors always as float32, integer tables as they are)."""
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
     architecture = resolve_architecture(config)
     parsed = architecture.parse(config)
     tensors = architecture.random_tensors(parsed, seed)
-    stored = {name: (t if t.dim() < 2 else t.to(dtype)).contiguous() for name, t in tensors.items()}
+    stored = {name: (t if t.dim() < 2 or not t.is_floating_point() else t.to(dtype)).contiguous() for name, t in tensors.items()}
     save_file(stored, str(folder / "model.safetensors"))
     (folder / "config.json").write_text(json.dumps(config, indent=1))
     return folder
