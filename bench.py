@@ -24,7 +24,10 @@ depth, heads and feed-forward, and each kernel of the new design alone against i
 the like kernel of Muse-Glimmer (`--size` picks one size). `--only dolutar` is the same kind of record for
 the Dolutar design (sliding-window attention with kept first positions and a sink, a clamped gated unit,
 routed experts), beside Muse-Glimmer with sliding attention at equal width, depth, heads, window and
-active feed-forward width.
+active feed-forward width. `--only bobarax` is that record for the Bobarax design (decayed linear attention,
+run-masked attention with capped scores, gated windowed attention, experts chosen by a table), beside Dolutar
+at equal width, depth, heads, window and experts; its kernels stand beside the like kernels of Dolutar and,
+for the recurrence, of Fokalorn.
 """
 
 from __future__ import annotations
@@ -1007,6 +1010,274 @@ def run_dolutar(args) -> dict:
     return record
 
 
+BOBARAX_SIZES = {
+    # width, heads x head size (keys and values alike), key/value heads, layers, window of the windowed layers,
+    # run length and cap of the run-masked layers, the dense feed-forward, experts of which `top` a token, an
+    # expert's feed-forward; `keep` and `identity` only shape the Dolutar model beside it
+    "1024": dict(width=1024, heads=16, dim=64, kv=4, layers=8, window=512, run=512, softcap=30.0, ff=4096, experts=16, top=2,
+                 eff=1024, keep=64, identity=2),
+    "2048": dict(width=2048, heads=16, dim=128, kv=4, layers=8, window=512, run=512, softcap=30.0, ff=8192, experts=32, top=4,
+                 eff=1536, keep=64, identity=4),
+    "4096": dict(width=4096, heads=32, dim=128, kv=8, layers=4, window=1024, run=1024, softcap=30.0, ff=12288, experts=16,
+                 top=4, eff=2048, keep=128, identity=2),
+}
+
+
+def bobarax_config(size: dict) -> dict:
+    """Layers in fours: a windowed layer with the dense feed-forward that owns a cache, a decayed
+    linear-attention layer with experts, a run-masked layer with experts, and a windowed layer with
+    experts that reads the first one's cache."""
+    H, G, d = size["heads"], size["kv"], size["dim"]
+    moe = {"kind": "moe", "expert": {"ff": size["eff"], "limit": 7.0}, "router": {"experts": size["experts"], "top": size["top"]}}
+    windowed = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": {"base": 100000.0, "dims": d // 2},
+                "mask": {"size": size["window"]}}
+    layers = []
+    for i in range(size["layers"]):
+        kind = i % 4
+        if kind == 0:
+            layers.append({"type": "attention_2", "mixer": dict(windowed), "mlp": {"kind": "dense", "ff": size["ff"]}})
+        elif kind == 1:
+            decay = [1.0 - 2.0 ** -(3 + 7 * h / max(H - 1, 1)) for h in range(H)]
+            layers.append({"type": "lightning", "mixer": {"heads": H, "dim": d, "vdim": d, "decay": decay}, "mlp": moe})
+        elif kind == 2:
+            layers.append({"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5,
+                                                          "softcap": size["softcap"], "mask": {"size": size["run"]}}, "mlp": moe})
+        else:
+            layers.append({"type": "attention_2", "mixer": dict(windowed, kv_from=i - 3), "mlp": moe})
+    return {"architecture": "Bobarax", "vocab": DOLUTAR_VOCAB, "width": size["width"], "residual_mult": 0.5, "logit_scale": 1.0,
+            "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def run_bobarax(args) -> dict:
+    """Prefill (one prompt of --prefill-tokens) and decode (--batch requests ending at --context tokens)
+    of Bobarax and of Dolutar at equal sizes, then the new design's kernels alone, each beside the like
+    kernel of Dolutar (attention, experts) or Fokalorn (the recurrence)."""
+    import torch
+
+    from mlx_omnia_b200.engine.engine import Engine, EngineArgs
+    from mlx_omnia_b200.engine.step import StepEntry
+    from mlx_omnia_b200.kernels import ops
+    from mlx_omnia_b200.parts.base import KVSpec, KVView
+
+    measured, peak_source = peaks()
+    hbm, flops_peak = measured["hbm_gbs"] * 1e9, measured["bf16_tflops"] * 1e12
+    g = torch.Generator().manual_seed(SEED)
+    steps, warmup, batch, context, tokens = args.steps, max(args.warmup, 3), args.batch, args.context, args.prefill_tokens
+    dev, bf = torch.device("cuda:0"), torch.bfloat16
+    vocab = DOLUTAR_VOCAB
+
+    def timed(fn, count, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(count):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / count
+
+    def whole_model(raw) -> dict:
+        engine = Engine.from_random(raw, SEED, EngineArgs(dtype="bfloat16", page_size=16, max_requests=batch + 1,
+                                                          cache_tokens=batch * (context + 16) + tokens + 16))
+        times = []
+        for index in range(warmup + 3):
+            request = engine.cache.open(f"p{index}")
+            ids = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.runner.run([StepEntry(request, ids, [tokens - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            engine.cache.close(request.request_id)
+            times.append(start.elapsed_time(stop))
+        prefill_ms = statistics.median(times[warmup:])
+        requests = [engine.cache.open(f"d{i}") for i in range(batch)]
+        length = context - steps - warmup - 1
+        for r in requests:
+            engine.runner.run([StepEntry(r, torch.randint(0, vocab, (length,), generator=g).tolist(), [])])
+        entries = lambda i: [StepEntry(r, [1 + i], [0]) for r in requests]
+        for i in range(warmup):
+            engine.runner.run(entries(i), copy=False)
+        torch.cuda.synchronize()
+        launches = ops.launches
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            engine.runner.run(entries(warmup + i), copy=False)
+        stop.record()
+        torch.cuda.synchronize()
+        decode_ms = start.elapsed_time(stop) / steps
+        ops.raise_on_error(engine.runtime.device)
+        out = {"prefill_tokens_per_s": round(tokens * 1000.0 / prefill_ms, 1), "prefill_ms": round(prefill_ms, 3),
+               "decode_tokens_per_s": round(batch * 1000.0 / decode_ms, 1), "decode_ms": round(decode_ms, 4),
+               "launches_per_decode_step": (ops.launches - launches) // steps}
+        for r in requests:
+            engine.cache.close(r.request_id)
+        del engine
+        torch.cuda.empty_cache()
+        return out
+
+    class Step:
+        pass
+
+    def step_of(lens, starts):
+        st = Step()
+        st.num_seqs, st.q_lens = len(lens), list(lens)
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        st.num_tokens = cu[-1]
+        st.cu_seqlens = torch.tensor(cu, dtype=torch.int32, device=dev)
+        st.state_slots = torch.arange(len(lens), dtype=torch.int32, device=dev)
+        st.positions = torch.tensor([s + i for s, n in zip(starts, lens) for i in range(n)], dtype=torch.int32, device=dev)
+        st.seq_lens = torch.tensor([s + n for s, n in zip(starts, lens)], dtype=torch.int32, device=dev)
+        st.seq_lens_host, st.max_q_len = [s + n for s, n in zip(starts, lens)], max(lens)
+        st.max_seq_len = max(st.seq_lens_host)
+        st.decode_only, st.workspace = all(n == 1 for n in lens), None
+        return st
+
+
+    def kernels(size: dict) -> dict:
+        H, G, d, D = size["heads"], size["kv"], size["dim"], size["width"]
+        window, run, cap = size["window"], size["run"], size["softcap"]
+        E, top, F = size["experts"], size["top"], size["eff"]
+        out = {}
+
+        def note(name, ms, bytes_=None, flops=None):
+            entry = {"us": round(ms * 1000.0, 2)}
+            if bytes_ is not None:
+                entry.update(gb_s=round(bytes_ / ms / 1e6, 1), frac_hbm=round(bytes_ / (ms / 1e3) / hbm, 4))
+            if flops is not None:
+                entry.update(tflops=round(flops / ms / 1e9, 2), frac_tensor=round(flops / (ms / 1e3) / flops_peak, 4))
+            out[name] = entry
+
+        for mode, lens, starts in (("prefill", [tokens], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+            st = step_of(lens, starts)
+            T = sum(lens)
+            page = 16
+            pages = -(-st.max_seq_len // page)
+            table = torch.arange(len(lens) * pages, dtype=torch.int32, device=dev).view(len(lens), pages)
+            slots = torch.cat([table[i].long()[(st.positions[st.cu_seqlens[i]: st.cu_seqlens[i + 1]] // page).long()] * page
+                               + st.positions[st.cu_seqlens[i]: st.cu_seqlens[i + 1]].long() % page for i in range(len(lens))])
+            cache = (torch.randn(len(lens) * pages, 2, G, page, d, device=dev) * 0.3).to(bf)
+            kv = KVView(cache, table, slots, page, window, True, KVSpec(((G, d), (G, d)), window))
+            run_kv = KVView(cache, table, slots, page, None, True, KVSpec(((G, d), (G, d)), None, chunk=run))
+            plain_kv = KVView(cache, table, slots, page, run, True, KVSpec.keys_and_values(G, d, run))
+            st.token_ids = torch.randint(0, vocab, (T,), device=dev, dtype=torch.int32)
+            # one norm over the whole projection, the rotation in neighbouring pairs over half a head, the cache
+            # write; beside the norm of every head by itself with the rotation in split halves
+            cols = (H + 2 * G) * d
+            proj = (torch.randn(T, cols + H * d, device=dev) * 0.5).to(bf)  # q | k | v | gate
+            inv = torch.tensor([100000.0 ** (-2.0 * i / (d // 2)) for i in range(d // 4)], device=dev)
+            wq, wk, wh = torch.ones(H * d, device=dev), torch.ones(G * d, device=dev), torch.ones(d, device=dev)
+            ms = timed(lambda: ops.qkv_prepare(proj, 0, H * d, (H + G) * d, H, d, None, wq, wk, 1e-5, inv, st.positions, kv, True,
+                                               whole=True, interleaved=True), 20)
+            note(f"qkv_prepare_whole_{mode}", ms, bytes_=T * cols * 4)
+            ms = timed(lambda: ops.qkv_prepare(proj, 0, H * d, (H + G) * d, H, d, None, wh, wh, 1e-5, inv, st.positions, kv, True), 20)
+            note(f"like:qkv_prepare_{mode}", ms, bytes_=T * cols * 4)
+            # attention: the window with the gate on the heads' outputs; the runs with capped scores beside a
+            # window as long as a run (which sees about twice the keys in a prompt: a run's queries see half a run
+            # on average)
+            q = (torch.randn(T, H, d, device=dev) * 0.3).to(bf)
+            sink = torch.zeros(H, device=dev)
+            reps = 5 if mode == "prefill" else 20
+
+            def pairs(visible):
+                return sum(visible(s + i) for s, n in zip(starts, lens) for i in range(n))
+
+            in_window, in_run = pairs(lambda p: min(p + 1, window)), pairs(lambda p: p % run + 1)
+            in_like = pairs(lambda p: min(p + 1, run))
+            held_w = sum(min(s + n, window + n - 1) for s, n in zip(starts, lens))
+            held_r = sum(min(s + n, (s % run) + n) for s, n in zip(starts, lens))
+            held_l = sum(min(s + n, run + n - 1) for s, n in zip(starts, lens))
+            moved = lambda held: held * 2 * G * d * 2 + 4 * T * H * d
+            ms = timed(lambda: ops.paged_attention(q, kv, st, d ** -0.5, gate=proj, gate_col=cols, window=window), reps, 2)
+            note(f"window_gate_attention_{mode}", ms, bytes_=moved(held_w) + 2 * T * H * d, flops=4 * in_window * H * d)
+            dolutar_kv = KVView(cache, table, slots, page, window, True, KVSpec(((G, d), (G, d)), window, keep_first=size["keep"]))
+            ms = timed(lambda: ops.paged_attention(q, dolutar_kv, st, d ** -0.5, sink=sink, window=window, keep_first=size["keep"]),
+                       reps, 2)
+            note(f"like:sink_window_attention_{mode}", ms, bytes_=moved(held_w), flops=4 * in_window * H * d)
+            ms = timed(lambda: ops.paged_attention(q, run_kv, st, d ** -0.5, window=None, chunk=run, softcap=cap), reps, 2)
+            note(f"run_capped_attention_{mode}", ms, bytes_=moved(held_r), flops=4 * in_run * H * d)
+            ms = timed(lambda: ops.paged_attention(q, run_kv, st, d ** -0.5, window=None, chunk=run), reps, 2)
+            note(f"run_attention_no_cap_{mode}", ms, bytes_=moved(held_r), flops=4 * in_run * H * d)
+            ms = timed(lambda: ops.paged_attention(q, plain_kv, st, d ** -0.5), reps, 2)
+            note(f"like:paged_attention_{mode}", ms, bytes_=moved(held_l), flops=4 * in_like * H * d)
+            # the decayed linear attention (activations, recurrence, norm over all heads, gate) beside the gated delta
+            # rule of equal heads and widths with the convolution ahead of it
+            lcols = 2 * H * d + 2 * H * d  # q | k | v | gate
+            lproj = (torch.randn(T, lcols, device=dev) * 0.5).to(bf)
+            S_state = torch.zeros(len(lens) + 1, H, d, d, device=dev)
+            decays = torch.full((H,), 0.99, device=dev)
+            nw = torch.ones(H * d, device=dev)
+            state_bytes = 2 * len(lens) * H * d * d * 4
+            ms = timed(lambda: ops.lightning_attention(lproj, 0, H * d, 2 * H * d, 3 * H * d, H, d, d, decays, nw, 1e-5, S_state, st), 10)
+            note(f"lightning_attention_{mode}", ms, bytes_=state_bytes + T * (4 * H * d * 2 + H * d * (4 + 4 + 2)),
+                 flops=T * H * d * d * 2 * 2)
+            C = 3 * H * d
+            dproj = torch.randn(T, C + H, device=dev).to(bf)
+            taps = torch.randn(C, 4, device=dev)
+            conv_state = torch.zeros(len(lens) + 1, 3, C, device=dev)
+            a, gate = torch.randn(T, H * d, device=dev).to(bf), torch.randn(T, H * d, device=dev).to(bf)
+            A_log, dt_bias, nwh = torch.zeros(H, device=dev), torch.zeros(H * d, device=dev), torch.ones(d, device=dev)
+            run_conv = lambda: ops.short_conv(dproj, 0, C, taps, conv_state, st, 2 * H * d, d, 1e-6, H * d, d ** -0.5,
+                                              a, A_log, dt_bias, C, H)
+            conv = run_conv()
+            note(f"like:short_conv_{mode}", timed(run_conv, 20), bytes_=T * (C * (2 + 4) + H * d * (2 + 4)))
+            S_state.zero_()
+            ms = timed(lambda: ops.delta_rule(conv, C, H, H, d, d, dproj, 0, gate, nwh, 1e-5, S_state, conv_state, 4, st), 10)
+            note(f"like:delta_rule_{mode}", ms, bytes_=state_bytes + T * ((C + H * d) * 4 + 2 * H * d * 2),
+                 flops=T * H * d * d * 2 * 3)
+            del S_state, lproj, dproj, conv
+            # the relu-gated unit in its product, beside SwiGLU in the same product
+            h = (torch.randn(T, D, device=dev) * 0.5).to(bf)
+            gate_up = (torch.randn(2 * size["ff"], D, device=dev) * D ** -0.5).to(bf)
+            dense = dict(bytes_=2 * size["ff"] * D * 2 + T * (D + size["ff"]) * 2, flops=2 * T * 2 * size["ff"] * D)
+            note(f"linear_relu_glu_{mode}", timed(lambda: ops.linear_relu_glu(h, gate_up), 10), **dense)
+            note(f"like:linear_swiglu_{mode}", timed(lambda: ops.linear_swiglu(h, gate_up), 10), **dense)
+            del gate_up
+            # experts chosen by the table (clamped units, equal weights) beside experts chosen by a router
+            egu = (torch.randn(E, 2 * F, D, device=dev) * D ** -0.5).to(bf)
+            edn = (torch.randn(E, D, F, device=dev) * F ** -0.5).to(bf)
+            rows = [torch.randperm(E, generator=g)[:top] for _ in range(4096)]
+            expert_table = torch.stack(rows).to(torch.int32).repeat(vocab // 4096, 1).to(dev).contiguous()
+            router, correction = torch.randn(E, D, device=dev) * 0.05, torch.zeros(E, device=dev)
+            counts = torch.zeros(E, dtype=torch.int32, device=dev)
+
+            def route_table():
+                counts.zero_()
+                return ops.moe_route_table(st.token_ids, expert_table, E, counts)
+
+            def route():
+                counts.zero_()
+                return ops.moe_route(h, router, correction, E, top, counts)
+
+            note(f"moe_route_table_{mode}", timed(route_table, 20), bytes_=T * (4 + top * 12))
+            note(f"like:moe_route_{mode}", timed(route, 20), bytes_=T * D * 2 + E * D * 4)
+            used = E * (1.0 - (1.0 - top / E) ** T)  # experts that T tokens' choices touch, on average
+            work = dict(bytes_=used * 3 * F * D * 2 + T * D * 4, flops=2 * T * top * 3 * F * D)
+            ms = timed(lambda: ops.moe_experts(h, None, None, egu, edn, top, st, table=expert_table, token_ids=st.token_ids,
+                                               alpha=1.702, limit=7.0), 10)
+            note(f"table_experts_{mode}", ms, **work)
+            ms = timed(lambda: ops.moe_experts(h, router, correction, egu, edn, top, st), 10)
+            note(f"like:routed_experts_{mode}", ms, **work)
+            del egu, edn
+        ops.raise_on_error(dev)
+        return out
+
+    record = {"metric": "Bobarax beside Dolutar at equal sizes", "unit": "tokens/s", "dtype": "bf16",
+              "data": "synthetic: seeded uniform-random token ids, random weights",
+              "config": {"prefill_tokens": tokens, "decode_batch": batch, "decode_context": context, "vocab": vocab,
+                         "peaks": peak_source}, "sizes": {}}
+    for name in ([args.size] if args.size else list(BOBARAX_SIZES)):
+        size = BOBARAX_SIZES[name]
+        record["sizes"][name] = {"bobarax": whole_model(bobarax_config(size)), "dolutar": whole_model(dolutar_config(size)),
+                                 "kernels": kernels(size), "layers": size["layers"]}
+    return record
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -1019,7 +1290,7 @@ def main() -> int:
                         help="with --only decode|prefill and OMNIA_TIMELINE=1 in the environment: one step's "
                              "kernels with the time each takes in the stream, on stderr")
     parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "portions", "sampling", "products", "elementwise", "fokalorn",
-                                           "dolutar"], default="all",
+                                           "dolutar", "bobarax"], default="all",
                         help="time one part only (small cases for profilers); prints a short record")
     parser.add_argument("--config", type=int, choices=sorted(CONFIGS), default=2,
                         help="with --only: the sizes of another benchmark configuration (3: 36 layers, hidden 4096, "
@@ -1031,7 +1302,7 @@ def main() -> int:
     parser.add_argument("--portion", type=int, default=256,
                         help="--only mixed: tokens of a prompt that run beside --batch decoding requests")
     parser.add_argument("--size", choices=sorted(FOKALORN_SIZES), default=None,
-                        help="--only fokalorn or dolutar: one size instead of all")
+                        help="--only fokalorn, dolutar or bobarax: one size instead of all")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -1047,6 +1318,9 @@ def main() -> int:
     args.context = args.context or CONFIGS[args.config][1]
     if args.only == "fokalorn":
         print(json.dumps(run_fokalorn(args)))
+        return 0
+    if args.only == "bobarax":
+        print(json.dumps(run_bobarax(args)))
         return 0
     if args.only == "dolutar":
         print(json.dumps(run_dolutar(args)))

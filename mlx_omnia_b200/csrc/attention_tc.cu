@@ -23,6 +23,9 @@
 // a softmax sink: `keep_first` (positions below it stay visible behind the window; the block that
 // owns the window's first keys walks the kept keys' tiles ahead of its own) and `sink` (one float
 // per query head: exp(sink) is added to the head's denominator when a row is finished).
+// Two more serve mixers whose queries read only their own run of positions and cap their scores:
+// `run` (a query at position i sees no key below i - i % run) and `softcap` (a scaled score s becomes
+// softcap * tanh(s / softcap) ahead of the softmax).
 #include "common.cuh"
 
 #ifndef HEAD_DIM
@@ -122,11 +125,12 @@ __device__ __forceinline__ const bf16* cache_row(const CacheRef& c, int pos, int
 //   row_lo/row_hi[2]: visible key range of the warp's rows g and g + 8 (inclusive; lo > hi: none)
 //   keep:    keys below it are visible whatever row_lo says (up to row_hi) ...
 //   floor:   ... unless they lie below this (they were attended to in a tile of their own)
+//   cap, pre: cap > 0: a raw score s becomes cap * tanh(s * pre) (pre = scale / cap; sl2 = log2(e))
 template <int NKEYS>
 __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16* ks, const bf16* vs,
                                             int key0, const int* row_lo, const int* row_hi,
                                             float sl2, float* m, float* l, float (*o)[4], int keep = 0,
-                                            int floor = 0) {
+                                            int floor = 0, float cap = 0.f, float pre = 0.f) {
   const int lane = threadIdx.x & 31;
   const int t = lane & 3;
   constexpr int NT = NKEYS / 8;
@@ -144,6 +148,13 @@ __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16*
       mma_bf16(s[2 * j2], qf[kstep], b0, b1);
       mma_bf16(s[2 * j2 + 1], qf[kstep], b2, b3);
     }
+  }
+  // Capped scores: s <- cap * tanh(s * pre) with pre = scale / cap; the caller's sl2 is then log2(e) alone.
+  if (cap > 0.f) {
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[j][e] = cap * tanhf(s[j][e] * pre);
   }
   // Mask, then the running maximum of rows g (elements 0,1) and g + 8 (elements 2,3).
   float mx[2] = {-INFINITY, -INFINITY};
@@ -233,7 +244,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
                          const int* __restrict__ seq_lens, const int* __restrict__ work,
                          const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out,
                          int max_pages, int num_pages, int nq, int nkv, int page_size, int window,
-                         float scale, int keep_first, const float* __restrict__ sink, int* err) {
+                         float scale, int keep_first, const float* __restrict__ sink, int run, float softcap,
+                         int* err) {
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][ROW]
@@ -260,7 +272,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
   }
 
   const int last = pos0 + tokens - 1;                                    // last key any row sees
-  const int first = window > 0 ? max(0, pos0 - window + 1) : 0;          // first key any row sees
+  int first = window > 0 ? max(0, pos0 - window + 1) : 0;                // first key any row sees
+  if (run > 0) first = max(first, pos0 - pos0 % run);                    // (the bound grows with the row's position)
   // The kept first positions that lie below every row's window come first, in tiles of their own.
   const int kept = min(keep_first, first);
   const int kept_tiles = (kept + BN - 1) / BN;
@@ -298,8 +311,10 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
     const int pos = pos0 + row / GROUP;
     row_hi[r] = row < rows ? pos : -1;
     row_lo[r] = row < rows ? (window > 0 ? max(0, pos - window + 1) : 0) : 0;
+    if (run > 0 && row < rows) row_lo[r] = max(row_lo[r], pos - pos % run);
   }
-  const float sl2 = scale * LOG2E;
+  const float sl2 = softcap > 0.f ? LOG2E : scale * LOG2E;
+  const float pre = softcap > 0.f ? scale / softcap : 0.f;
 
   for (int tile = 0; tile < tiles; ++tile) {
     if (tile + 1 < tiles) load_tile(tile + 1, (tile + 1) & 1);
@@ -313,9 +328,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
     const int warp_last = pos0 + min(rows - 1, warp * 16 + 15) / GROUP;
     if (warp * 16 < rows && tile < kept_tiles) {
       const int all[2] = {0, 0}, below[2] = {min(row_hi[0], kept - 1), min(row_hi[1], kept - 1)};
-      attend_tile<BN>(qf, kt, kt + BN * ROW, key0, all, below, sl2, m, l, o);
+      attend_tile<BN>(qf, kt, kt + BN * ROW, key0, all, below, sl2, m, l, o, 0, 0, softcap, pre);
     } else if (warp * 16 < rows && key0 <= warp_last) {
-      attend_tile<BN>(qf, kt, kt + BN * ROW, key0, row_lo, row_hi, sl2, m, l, o, keep_first, kept);
+      attend_tile<BN>(qf, kt, kt + BN * ROW, key0, row_lo, row_hi, sl2, m, l, o, keep_first, kept, softcap, pre);
     }
     __syncthreads();
   }
@@ -468,7 +483,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
                         int* __restrict__ tickets, const bf16* __restrict__ gate, int gate_stride,
                         bf16* __restrict__ out, int chunk_keys, int max_chunks, int max_pages,
                         int num_pages, int nq, int nkv, int page_size, int window, float scale,
-                        const FusedQK fused, int keep_first, const float* __restrict__ sink, int* err) {
+                        const FusedQK fused, int keep_first, const float* __restrict__ sink, int run, float softcap,
+                        int* err) {
   // In the fused mode nothing up to the query fragments depends on the kernel before this one
   // (the lengths and tables were copied in before the step began, the keys and values of earlier
   // tokens were written in earlier steps), so the block's start and its first loads of the cache
@@ -483,7 +499,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   const int seq = seq_ids ? seq_ids[blockIdx.z] : blockIdx.z;
   const int kvh = blockIdx.y, chunk = blockIdx.x;
   const int pos = seq_lens[seq] - 1;
-  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  int first = window > 0 ? max(0, pos - window + 1) : 0;
+  if (run > 0 && pos >= 0) first = max(first, pos - pos % run);
   const int lo = max(first, chunk * chunk_keys), hi = min(pos, (chunk + 1) * chunk_keys - 1);
   if (pos < 0 || lo > hi) {
     if (early) pdl_wait();
@@ -671,7 +688,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     row_lo[r] = lo;
     row_hi[r] = row < GROUP ? hi : -1;
   }
-  const float sl2 = scale * LOG2E;
+  const float sl2 = softcap > 0.f ? LOG2E : scale * LOG2E;
+  const float pre = softcap > 0.f ? scale / softcap : 0.f;
 
   for (int tile = 0; tile < tiles; ++tile) {
     if (FILLED) {
@@ -697,9 +715,11 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     }
     if (warp + tile * WARPS < kept_tiles) {
       const int all[2] = {0, 0}, below[2] = {min(row_hi[0], kept - 1), min(row_hi[1], kept - 1)};
-      attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, tile_of(tile) * DECODE_BN, all, below, sl2, m, l, o);
+      attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, tile_of(tile) * DECODE_BN, all, below, sl2, m, l, o, 0, 0,
+                             softcap, pre);
     } else {
-      attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, tile_of(tile) * DECODE_BN, row_lo, row_hi, sl2, m, l, o);
+      attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, tile_of(tile) * DECODE_BN, row_lo, row_hi, sl2, m, l, o, 0, 0,
+                             softcap, pre);
     }
     __syncwarp();
     if (STAGES == 1) {  // the one stage is free again
@@ -822,9 +842,12 @@ extern "C" int omnia_attention_prefill_tc(const void* q, const void* pages, cons
                                           const int* work, int blocks, const void* gate,
                                           int gate_stride, void* out, int max_pages, int num_pages,
                                           int nq, int nkv, int page_size, int window, float scale,
-                                          int keep_first, const float* sink, int* err, cudaStream_t stream) {
+                                          int keep_first, const float* sink, int run, float softcap, int* err,
+                                          cudaStream_t stream) {
   if (blocks == 0) return 0;
-  if (nq != nkv * GROUP || keep_first < 0 || (keep_first > 0 && window <= 0)) return (int)cudaErrorInvalidValue;
+  if (nq != nkv * GROUP || keep_first < 0 || (keep_first > 0 && window <= 0) || run < 0 || softcap < 0.f ||
+      (run > 0 && keep_first > 0))
+    return (int)cudaErrorInvalidValue;
   const size_t smem = (size_t)(BM + 4 * BN) * ROW * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
@@ -835,7 +858,8 @@ extern "C" int omnia_attention_prefill_tc(const void* q, const void* pages, cons
   }
   launch_pdl(attention_prefill_kernel, dim3(blocks, nkv), 128, smem, stream, 
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate,
-      gate_stride, (bf16*)out, max_pages, num_pages, nq, nkv, page_size, window, scale, keep_first, sink, err);
+      gate_stride, (bf16*)out, max_pages, num_pages, nq, nkv, page_size, window, scale, keep_first, sink, run,
+      softcap, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -857,10 +881,11 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
                                          int page_size, int window, float scale, int warps,
                                          const void* proj, int proj_stride, int q_col, int k_col, int v_col,
                                          float eps, const float* inv_freq, const long long* slot_mapping,
-                                         int spread, int keep_first, const float* sink, int* err,
-                                         cudaStream_t stream) {
+                                         int spread, int keep_first, const float* sink, int run, float softcap,
+                                         int* err, cudaStream_t stream) {
   if (requests == 0) return 0;
   if (keep_first < 0 || (keep_first > 0 && (window <= 0 || proj != nullptr))) return (int)cudaErrorInvalidValue;
+  if (run < 0 || softcap < 0.f || (run > 0 && keep_first > 0)) return (int)cudaErrorInvalidValue;
   if (requests < 0 || nkv < 1 || nq != nkv * GROUP || chunk_keys <= 0 || chunk_keys % DECODE_BN != 0 ||
       max_chunks < 1 || max_pages < 1 || num_pages < 1 || page_size < 1 || (warps != 1 && warps != 4))
     return (int)cudaErrorInvalidValue;
@@ -904,17 +929,17 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
     launch_pdl(attention_decode_kernel<1, DECODE_STAGES>, dim3(max_chunks, nkv, requests), 32, smem, stream,
         (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
         tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-        num_pages, nq, nkv, page_size, window, scale, fused, keep_first, sink, err);
+        num_pages, nq, nkv, page_size, window, scale, fused, keep_first, sink, run, softcap, err);
   else if (deep)
     launch_pdl(attention_decode_kernel<4, 2>, dim3(max_chunks, nkv, requests), 128, smem, stream,
         (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
         tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-        num_pages, nq, nkv, page_size, window, scale, fused, keep_first, sink, err);
+        num_pages, nq, nkv, page_size, window, scale, fused, keep_first, sink, run, softcap, err);
   else
     launch_pdl(attention_decode_kernel<4, 1>, dim3(max_chunks, nkv, requests), 128, smem, stream,
         (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
         tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-        num_pages, nq, nkv, page_size, window, scale, fused, keep_first, sink, err);
+        num_pages, nq, nkv, page_size, window, scale, fused, keep_first, sink, run, softcap, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -1008,7 +1033,7 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
   launch_pdl(attention_decode_kernel<1, DECODE_STAGES>, dim3(max_chunks, nkv, requests), 32, smem, stream,
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
       ticket_area, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-      num_pages, nq, nkv, page_size, window, scale, FusedQK{}, 0, nullptr, err);
+      num_pages, nq, nkv, page_size, window, scale, FusedQK{}, 0, nullptr, 0, 0.f, err);
   e = cudaGetLastError();
   if (e != cudaSuccess) snprintf(static_error, sizeof static_error, "launch: %s", cudaGetErrorString(e));
   return (int)e;

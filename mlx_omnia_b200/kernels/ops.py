@@ -636,10 +636,11 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
     gate_stride = 0 if gate is None else gate.shape[1]
     err = _ptr(error_word(q.device))
     max_pages, num_pages = kv.block_table.shape[1], kv.pages.shape[0]
-    chunk, softcap = int(chunk or 0), float(softcap or 0.0)
-    if chunk and keep:
+    run, softcap = int(chunk or 0), float(softcap or 0.0)
+    if run and keep:
         raise KernelError("a mask of runs keeps no first positions")
-    if dv != d or not tiled_attention_supported(q.dtype, nq, nkv, d) or chunk or softcap:
+    tcgen05_ok = not run and not softcap  # the tcgen05 prefill kernels take neither
+    if dv != d or not tiled_attention_supported(q.dtype, nq, nkv, d):
         if projection is not None:
             raise KernelError("the generic attention kernel takes queries, not projected rows")
         fn = _function("attention_generic", "omnia_paged_attention_generic",
@@ -648,7 +649,7 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
                         c_int, c_float, c_int, c_float, c_int, c_void_p, c_void_p])
         _check(fn(_ptr(q), k_ptr, v_ptr, page_stride, _ptr(kv.block_table), _ptr(step.cu_seqlens),
                   _ptr(step.positions), gate_ptr, gate_stride, _ptr(out), _ptr(sink), tokens, step.num_seqs, max_pages,
-                  num_pages, nq, nkv, d, dv, kv.page_size, kv.window or 0, keep, scale, chunk, softcap,
+                  num_pages, nq, nkv, d, dv, kv.page_size, kv.window or 0, keep, scale, run, softcap,
                   _code(q.dtype), err, _stream()), "paged_attention")
         return out
     defines = {"HEAD_DIM": d, "GROUP": nq // nkv}
@@ -668,7 +669,7 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
                        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_float, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
-                        c_int, c_int, c_void_p, c_void_p, c_void_p], defines)
+                        c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p], defines)
         p = projection
         fused = (None, 0, 0, 0, 0, -1.0, None, None) if p is None else (
             _ptr(p.rows), p.rows.shape[1], p.q_col, p.k_col, p.v_col, -1.0 if p.eps is None else p.eps,
@@ -676,10 +677,11 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
         _check(fn(None if p is not None else _ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens),
                   _ptr(step.seq_lens), _ptr(single), count, _ptr(part_o), _ptr(part_ml), _ptr(tickets), chunk,
                   max_chunks, gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size,
-                  kv.window or 0, scale, warps, *fused, 1, keep, _ptr(sink), err, _stream()), "attention_decode")
+                  kv.window or 0, scale, warps, *fused, 1, keep, _ptr(sink), run, softcap, err, _stream()),
+               "attention_decode")
         if step.decode_only or all(n == 1 for n in step.q_lens):
             return out
-    if tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
+    if tcgen05_ok and tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
         per_block = 128 // (nq // nkv)
         sms = sm_count(q.device)
         plain = sink is None and not keep  # a sink or kept first positions: the two-to-an-SM kernel, every block whole
@@ -718,10 +720,11 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
     work = _prefill_work(step, tokens_per_block, q.device)
     fn = _function("attention_tc", "omnia_attention_prefill_tc",
                    [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
-                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p], defines)
+                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_float, c_void_p,
+                    c_void_p], defines)
     _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens), _ptr(work),
               work.shape[0], gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size,
-              kv.window or 0, scale, keep, _ptr(sink), err, _stream()), "attention_prefill")
+              kv.window or 0, scale, keep, _ptr(sink), run, softcap, err, _stream()), "attention_prefill")
     return out
 
 

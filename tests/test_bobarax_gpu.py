@@ -187,9 +187,9 @@ def test_a_boosted_key_just_inside_and_just_outside(dtype, H, G, dk, dv, page):
     back, in a prompt and in single tokens."""
     g = torch.Generator().manual_seed(7)
     dt, N = DTYPES[dtype], 420
-    for window, chunk, query, key, inside in [(96, None, 400, 305, True), (96, None, 400, 304, False),
-                                              (None, 120, 400, 360, True), (None, 120, 400, 359, False),
-                                              (None, 120, 359, 240, True), (None, None, 419, 3, True),
+    for window, chunk, query, key, inside in [(100, None, 400, 301, True), (100, None, 400, 300, False),
+                                              (None, 112, 400, 336, True), (None, 112, 400, 335, False),
+                                              (None, 112, 335, 224, True), (None, None, 419, 3, True),
                                               (257, None, 300, 44, True), (257, None, 300, 43, False)]:
         K, V = torch.randn(N, G, dk, generator=g) * 0.1, torch.randn(N, G, dv, generator=g)
         direction = torch.randn(dk, generator=g)
