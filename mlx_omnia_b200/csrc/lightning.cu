@@ -11,11 +11,15 @@
 //
 // The recurrence kernel is sequential in a request's tokens and parallel over (request, head, run
 // of value columns): the columns of S are independent. A column is held by P threads, each with
-// DK / P of its rows in registers; between tokens there are only shuffles inside a warp. The
-// activations are taken in float32 and rounded to the element type, as a product with the
-// activation in its epilogue would store them; the state, the decay and every sum stay float32.
-// It serves decode steps (one token a request) and prompts' portions of any length alike; the
-// order of a column's additions does not depend on how a prompt was cut.
+// DK / P of its rows in registers. The block's other warps are loaders: while the column threads walk
+// one run of LIGHTNING_CHUNK tokens out of shared memory, the loaders fetch the next run's projected
+// rows, apply the activations in float32, round them to the element type, as a product with the
+// activation in its epilogue would store them, and leave them in the other half of a double buffer; the
+// two sides meet at one barrier a run. A token's partial sums stay in registers until its run is done,
+// so the shuffles that add them up are off the chain from token to token, which is one fused
+// multiply-add a row. The state, the decay and every sum stay float32. It serves decode steps (one
+// token a request) and prompts' portions of any length alike; the order of a column's additions does
+// not depend on how a prompt was cut.
 //
 // Compiled per key width: -DLIGHTNING_DK=<DK>.
 #include "common.cuh"
@@ -23,17 +27,19 @@
 #ifndef LIGHTNING_DK
 #define LIGHTNING_DK 64
 #endif
-#define LIGHTNING_CHUNK 16  // tokens staged in shared memory at a time
+#define LIGHTNING_CHUNK 16     // tokens staged in shared memory at a time
+#define LIGHTNING_LOADERS 128  // threads of a block that stage the next tokens while the others walk these
+#define LIGHTNING_THREADS 512  // of a block at most: 128 registers a thread for the state's rows
 
 namespace {
 
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.f + expf(-x)); }
 
 template <typename T, int P>
-__global__ void __launch_bounds__(1024) lightning_recurrence_kernel(
+__global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel(
     const T* __restrict__ proj, int stride, int q_col, int k_col, int v_col, int H, int dv, int cols, int parts,
-    const float* __restrict__ decay, float* __restrict__ S_state, const int* __restrict__ cu_seqlens,
-    const int* __restrict__ state_slots, float* __restrict__ o_raw) {
+    int column_threads, const float* __restrict__ decay, float* __restrict__ S_state,
+    const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, float* __restrict__ o_raw) {
   pdl_wait();
   pdl_launch_dependents();
   constexpr int DK = LIGHTNING_DK;
@@ -42,58 +48,88 @@ __global__ void __launch_bounds__(1024) lightning_recurrence_kernel(
   constexpr int VROW = P * SEG;  // floats of one token's vector of DK
   constexpr int TC = LIGHTNING_CHUNK;
   extern __shared__ float shared[];
-  float* qs = shared;            // [TC][VROW]
-  float* ks = qs + TC * VROW;    // [TC][VROW]
-  float* vs = ks + TC * VROW;    // [TC][cols]
+  const int half = 2 * TC * VROW + TC * cols;  // floats of one buffer: q [TC][VROW] | k [TC][VROW] | v [TC][cols]
   const int head = blockIdx.x / parts, part = blockIdx.x % parts, seq = blockIdx.y;
   const int col0 = part * cols;
   const int begin = cu_seqlens[seq], end = cu_seqlens[seq + 1];
   if (end <= begin) return;
-  const int slot = state_slots[seq];
+  const bool loader = (int)threadIdx.x >= column_threads;
+  const int loaders = (int)blockDim.x - column_threads, lt = (int)threadIdx.x - column_threads;
   const int j = threadIdx.x / P, p = threadIdx.x % P;
-  const bool live = j < cols && col0 + j < dv;
+  const bool live = !loader && j < cols && col0 + j < dv;
   const float lambda = decay[head];
 
+  // Tokens [t0, t0 + n) into buffer `buf`: activations in float32, rounded to the element type.
+  auto stage = [&](int t0, int n, float* buf) {
+    float* qs = buf;
+    float* ks = buf + TC * VROW;
+    float* vs = ks + TC * VROW;
+#pragma unroll 4
+    for (int idx = lt; idx < n * DK; idx += loaders) {
+      const int tok = idx / DK, i = idx % DK;
+      const T* src = proj + (size_t)(t0 + tok) * stride + head * DK + i;
+      const float q = to_f32(src[q_col]), k = to_f32(src[k_col]);
+      const int at = tok * VROW + (i / R) * SEG + i % R;
+      qs[at] = to_f32(from_f32<T>(silu_f32(q)));
+      ks[at] = to_f32(from_f32<T>(silu_f32(k)));
+    }
+#pragma unroll 4
+    for (int idx = lt; idx < n * cols; idx += loaders) {
+      const int tok = idx / cols, c = idx % cols;
+      vs[idx] = col0 + c < dv
+                    ? to_f32(from_f32<T>(silu_f32(to_f32(proj[(size_t)(t0 + tok) * stride + v_col + head * dv + col0 + c]))))
+                    : 0.f;
+    }
+  };
+
   float S[R];
-  float* mine = S_state + (((size_t)slot * H + head) * DK) * dv + col0 + j;
+  float* mine = S_state + (((size_t)state_slots[seq] * H + head) * DK) * dv + col0 + j;
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     const int r = p * R + i;
     S[i] = (live && r < DK) ? mine[(size_t)r * dv] : 0.f;
   }
 
-  for (int t0 = begin; t0 < end; t0 += TC) {
+  const int runs = (end - begin + TC - 1) / TC;
+  if (loader) stage(begin, min(TC, end - begin), shared);
+  __syncthreads();
+  for (int c = 0; c < runs; ++c) {
+    const int t0 = begin + c * TC;
     const int n = min(TC, end - t0);
-    __syncthreads();  // the chunk before has been read
-    for (int idx = threadIdx.x; idx < n * DK; idx += blockDim.x) {
-      const int tok = idx / DK, i = idx % DK;
-      const T* src = proj + (size_t)(t0 + tok) * stride + head * DK + i;
-      const int at = tok * VROW + (i / R) * SEG + i % R;
-      qs[at] = to_f32(from_f32<T>(silu_f32(to_f32(src[q_col]))));
-      ks[at] = to_f32(from_f32<T>(silu_f32(to_f32(src[k_col]))));
-    }
-    for (int idx = threadIdx.x; idx < n * cols; idx += blockDim.x) {
-      const int tok = idx / cols, c = idx % cols;
-      vs[idx] = col0 + c < dv
-                    ? to_f32(from_f32<T>(silu_f32(to_f32(proj[(size_t)(t0 + tok) * stride + v_col + head * dv + col0 + c]))))
-                    : 0.f;
-    }
-    __syncthreads();
-    for (int tok = 0; tok < n; ++tok) {
-      const float* kt = ks + tok * VROW + p * SEG;
-      const float* qt = qs + tok * VROW + p * SEG;
-      const float v = live ? vs[tok * cols + j] : 0.f;
-      float o = 0.f;
+    if (loader) {
+      if (c + 1 < runs) stage(t0 + TC, min(TC, end - t0 - TC), shared + ((c + 1) & 1) * half);
+    } else {
+      const float* qs = shared + (c & 1) * half;
+      const float* ks = qs + TC * VROW;
+      const float* vs = ks + TC * VROW;
+      float sums[TC];
 #pragma unroll
-      for (int i = 0; i < R; ++i)
-        if (p * R + i < DK) {
-          S[i] = lambda * S[i] + kt[i] * v;
-          o += S[i] * qt[i];
+      for (int tok = 0; tok < TC; ++tok) {
+        sums[tok] = 0.f;
+        if (tok < n) {
+          const float* kt = ks + tok * VROW + p * SEG;
+          const float* qt = qs + tok * VROW + p * SEG;
+          const float v = live ? vs[tok * cols + j] : 0.f;
+          float o = 0.f;
+#pragma unroll
+          for (int i = 0; i < R; ++i)
+            if (p * R + i < DK) {
+              S[i] = fmaf(kt[i], v, lambda * S[i]);
+              o = fmaf(S[i], qt[i], o);
+            }
+          sums[tok] = o;
         }
+      }
 #pragma unroll
-      for (int w = 1; w < P; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-      if (live && p == 0) o_raw[(size_t)(t0 + tok) * H * dv + head * dv + col0 + j] = o;
+      for (int tok = 0; tok < TC; ++tok)
+        if (tok < n) {
+          float o = sums[tok];
+#pragma unroll
+          for (int w = 1; w < P; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+          if (live && p == 0) o_raw[(size_t)(t0 + tok) * H * dv + head * dv + col0 + j] = o;
+        }
     }
+    __syncthreads();  // the next run is staged, this one has been read
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
@@ -128,7 +164,7 @@ extern "C" int omnia_lightning_dk(void) { return LIGHTNING_DK; }
 // proj: the projected rows [tokens, stride] with q at q_col, k at k_col (heads * DK each) and v at
 // v_col (heads * dv); decay float32 [heads]; S_state float32 [slots, heads, DK, dv], updated in place;
 // o_raw float32 [tokens, heads * dv] receives the unnormed outputs. parts: runs of columns a head is
-// cut into (dv must divide into them).
+// cut into (dv must divide into them; a run of at most 384 columns, 96 for four threads a column).
 extern "C" int omnia_lightning_recurrence(const void* proj, int stride, int q_col, int k_col, int v_col, int H, int dv,
                                           int parts, const float* decay, float* S_state, const int* cu_seqlens,
                                           const int* state_slots, int num_seqs, float* o_raw, int dtype,
@@ -140,18 +176,20 @@ extern "C" int omnia_lightning_recurrence(const void* proj, int stride, int q_co
 #define OMNIA_LIGHTNING_LAUNCH(P)                                                                              \
   do {                                                                                                         \
     constexpr int R = (LIGHTNING_DK + P - 1) / P;                                                              \
-    const size_t smem = sizeof(float) * ((size_t)2 * LIGHTNING_CHUNK * P * (R + 1) + LIGHTNING_CHUNK * cols);  \
+    const size_t smem = sizeof(float) * 2 * ((size_t)2 * LIGHTNING_CHUNK * P * (R + 1) + LIGHTNING_CHUNK * cols); \
     if (smem > 48 * 1024 && cudaFuncSetAttribute(lightning_recurrence_kernel<T, P>,                            \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
       return (int)cudaGetLastError();                                                                          \
-    launch_pdl(lightning_recurrence_kernel<T, P>, grid, dim3((cols * P + 31) / 32 * 32), smem, stream,         \
-               (const T*)proj, stride, q_col, k_col, v_col, H, dv, cols, parts, decay, S_state, cu_seqlens,    \
-               state_slots, o_raw);                                                                            \
+    const int column_threads = (cols * P + 31) / 32 * 32;                                                      \
+    launch_pdl(lightning_recurrence_kernel<T, P>, grid, dim3(column_threads + LIGHTNING_LOADERS), smem, stream, \
+               (const T*)proj, stride, q_col, k_col, v_col, H, dv, cols, parts, column_threads, decay, S_state, \
+               cu_seqlens, state_slots, o_raw);                                                                \
   } while (0)
+  constexpr int ROOM = LIGHTNING_THREADS - LIGHTNING_LOADERS;  // threads left for the columns
   OMNIA_DISPATCH_DTYPE(dtype, {
-    if (cols * 4 <= 1024 && LIGHTNING_DK >= 16) OMNIA_LIGHTNING_LAUNCH(4);
-    else if (cols * 2 <= 1024 && LIGHTNING_DK >= 8) OMNIA_LIGHTNING_LAUNCH(2);
-    else if (cols <= 1024) OMNIA_LIGHTNING_LAUNCH(1);
+    if (cols * 4 <= ROOM && LIGHTNING_DK >= 16) OMNIA_LIGHTNING_LAUNCH(4);
+    else if (cols * 2 <= ROOM && LIGHTNING_DK >= 8) OMNIA_LIGHTNING_LAUNCH(2);
+    else if (cols <= ROOM) OMNIA_LIGHTNING_LAUNCH(1);
     else return (int)cudaErrorInvalidValue;
   });
 #undef OMNIA_LIGHTNING_LAUNCH

@@ -1257,18 +1257,25 @@ def delta_rule(conv: torch.Tensor, channels: int, groups: int, heads: int, dk: i
 
 
 def lightning_parts(requests: int, heads: int, dv: int, sms: int) -> int:
-    """Into how many runs of columns the recurrence kernel cuts a head's value channels: the fewest
-    equal runs (of at least 8 columns) that give every SM a block, 1 when (request, head) pairs
-    alone do."""
+    """Into how many runs of columns the recurrence kernel cuts a head's value channels: at least as
+    many as bring a run down to 96 columns (four threads a column then fit a block; 192 and 384 where
+    dv divides no better), and beyond that the fewest equal runs (of at least 8 columns) that give
+    every SM a block when (request, head) pairs alone do not."""
+    divisors = [parts for parts in range(1, dv + 1) if dv % parts == 0]
+    least = next((parts for limit in (96, 192, 384) for parts in divisors if 8 <= dv // parts <= limit or
+                  (dv // parts <= limit and parts == 1)), None)
+    if least is None:
+        least = next(parts for parts in divisors if dv // parts <= 96)
     blocks = requests * heads
-    best = 1
-    for parts in range(1, dv + 1):
-        if dv % parts or dv // parts < 8:
-            continue
-        best = parts
-        if blocks * parts >= sms:
-            break
-    return best if blocks < sms else 1
+    best = least
+    if blocks < sms:
+        for parts in divisors:
+            if parts < least or dv // parts < 8:
+                continue
+            best = parts
+            if blocks * parts >= sms:
+                break
+    return best
 
 
 def lightning_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gate_col: int, heads: int, dk: int,
