@@ -33,6 +33,11 @@
 // parts in their order (the result does not depend on which part came last), normalises, applies
 // the gate and stores. Nobody waits for another block.
 //
+// Two more masks and one more step of the scores serve other mixers: `run` (a query at position i sees
+// no key below i - i % run; a block's first tile is the run's start of its first row, every row masks
+// below its own) and `softcap` (a scaled score s becomes softcap * tanh(s / softcap), in float32, in the
+// softmax warps ahead of the maximum: two more special-function operations a score).
+//
 // Every wait on a barrier is bounded: when the bound is hit the block raises OMNIA_ERR_TIMEOUT
 // in the error word, every role leaves its loop, the producer waits (bounded) for loads in
 // flight, the block frees its tensor memory and returns.
@@ -87,7 +92,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out,
                                  float* __restrict__ partial, int* __restrict__ tickets,
                                  int max_pages, int num_pages, int nq, int nkv, int page_size, int window,
-                                 float scale, int keep_first, const float* __restrict__ sink, int* err) {
+                                 float scale, int keep_first, const float* __restrict__ sink, int run, float softcap,
+                                 int* err) {
   if (work[WORK_INTS * blockIdx.x] < 0) return;  // a place of the list that this step does not use
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // The swizzled tiles need a base on 1024 bytes; the dynamic area starts on one (nothing static
@@ -115,7 +121,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int tokens = min(TOKENS, q_len - tok0);
   const int rows = tokens * GROUP;
   const int last = pos0 + tokens - 1;                                   // last key any row sees
-  const int first = window > 0 ? max(0, pos0 - window + 1) : 0;         // first key any row sees
+  int first = window > 0 ? max(0, pos0 - window + 1) : 0;               // first key any row sees
+  if (run > 0) first = max(first, pos0 - pos0 % run);                   // (a row sees no key ahead of its own run)
   const int last_tile = last / BN;
   // Kept first positions (a window that leaves the first `keep_first` positions visible): when some
   // row's window begins after position 0, the block first walks the tiles of the kept keys (every row
@@ -308,9 +315,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // 85 us a layer against 63 for 3,008).
     const int pos = min(pos0 + row / GROUP, last);
     const int row_hi = pos;
-    const int row_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int row_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (run > 0) row_lo = max(row_lo, pos - pos % run);
     const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
-    const float sl2 = scale * LOG2E;
+    // Capped scores: a raw score s becomes cap * tanh(s * scale / cap), here at once in units of the
+    // exponent (times log2 e), so that everything below goes on with a scale of 1. tanh(x) is taken as
+    // 1 - 2 / (exp2(2 log2(e) x) + 1): its absolute error is a few units of 2^-24, whatever x.
+    const bool capped = softcap > 0.f;
+    const float sl2 = capped ? 1.f : scale * LOG2E;
+    const float cap2 = softcap * LOG2E, cap_in = capped ? 2.f * LOG2E * scale / softcap : 0.f;
     float m = -INFINITY, l = 0.f;
     bool ok = true, gate_issued = false;
     for (int j = 0; j < n_tiles && ok; ++j) {
@@ -341,6 +354,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       tmem_load32(s_addr, v);
       tmem_load32(s_addr + 32, v + 32);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (capped) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          v[i] = __float_as_uint(fmaf(-2.f * cap2, fast_rcp(fast_exp2(__uint_as_float(v[i]) * cap_in) + 1.f), cap2));
+      }
       float tile_max = -INFINITY;
       if (unmasked) {
         float part[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one of 64
@@ -641,11 +659,11 @@ extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const 
                                                int blocks, const void* gate, int gate_stride, void* out,
                                                float* partial, int* tickets,
                                                int max_pages, int num_pages, int nq, int nkv, int page_size,
-                                               int window, float scale, int keep_first, const float* sink, int* err,
-                                               cudaStream_t stream) {
+                                               int window, float scale, int keep_first, const float* sink, int run,
+                                               float softcap, int* err, cudaStream_t stream) {
   if (blocks == 0) return 0;
   if (nq != nkv * GROUP || page_size % 16 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)pages & 15) || keep_first < 0 ||
-      (keep_first > 0 && window <= 0))
+      (keep_first > 0 && window <= 0) || run < 0 || softcap < 0.f || (run > 0 && keep_first > 0))
     return (int)cudaErrorInvalidValue;
   CUtensorMap map_q, map_kv, map_gate;
   int gate_tma = 0;
@@ -662,6 +680,7 @@ extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const 
   }
   launch_pdl(attention_prefill_tcgen05_kernel, blocks, THREADS, smem, stream,
              map_q, map_kv, map_gate, gate_tma, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate, gate_stride, (bf16*)out,
-             partial, tickets, max_pages, num_pages, nq, nkv, page_size, window, scale, keep_first, sink, err);
+             partial, tickets, max_pages, num_pages, nq, nkv, page_size, window, scale, keep_first, sink, run, softcap,
+             err);
   return OMNIA_LAUNCH_RESULT();
 }

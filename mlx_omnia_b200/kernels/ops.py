@@ -448,7 +448,7 @@ def prefill_blocks(step: StepContext, tokens_per_block: int, nkv: int) -> int:
 
 
 def prefill_work_table(q_lens, seq_lens, tokens_per_block: int, tile: int, nkv: int, window: int, places: int,
-                       capacity: int | None = None) -> np.ndarray:
+                       capacity: int | None = None, run: int = 0) -> np.ndarray:
     """The tcgen05 prefill kernel's list, int32 [blocks, 8]: (request, first token, key/value head, first
     key tile of the part, tiles of the part (-1: all), parts + 256 * part, place of the block's first
     part in the workspace, number of the block among the split ones), the longest first: blocks are
@@ -471,6 +471,8 @@ def prefill_work_table(q_lens, seq_lens, tokens_per_block: int, tile: int, nkv: 
             pos0 = seq_lens[s] - n + t0
             last = pos0 + np.minimum(tokens_per_block, n - t0) - 1
             first = np.maximum(0, pos0 - window + 1) if window else np.zeros_like(t0)
+            if run:  # a block's rows see no key ahead of the run of its first row
+                first = np.maximum(first, pos0 - pos0 % run)
             tiles = last // tile - first // tile + 1
         # Every block of tokens once per key/value head, heads innermost.
         blocks.append(np.stack([np.repeat(tiles, nkv), np.full(t0.size * nkv, s), np.repeat(t0, nkv),
@@ -539,11 +541,12 @@ def wide_prefill_pays(q_lens, seq_lens, tokens_per_block: int, nkv: int, window:
 
 
 def _prefill_work_flat(step: StepContext, tokens_per_block: int, tile: int, nkv: int, window: int,
-                       device: torch.device, places: int) -> torch.Tensor:
-    """The list of `prefill_work_table` for this step, made once and shared by the layers of equal window."""
+                       device: torch.device, places: int, run: int = 0) -> torch.Tensor:
+    """The list of `prefill_work_table` for this step, made once and shared by the layers of equal window and run."""
     capacity = prefill_blocks(step, tokens_per_block, nkv) + places if (step.workspace or {}).get("private") else None
-    build = lambda st: prefill_work_table(st.q_lens, st.seq_lens_host, tokens_per_block, tile, nkv, window, places, capacity)
-    return _step_list(step, ("prefill_work_flat", tokens_per_block, tile, nkv, window, places), build, device)
+    build = lambda st: prefill_work_table(st.q_lens, st.seq_lens_host, tokens_per_block, tile, nkv, window, places, capacity,
+                                          run)
+    return _step_list(step, ("prefill_work_flat", tokens_per_block, tile, nkv, window, places, run), build, device)
 
 
 def single_token_longest(step: StepContext) -> int:
@@ -611,7 +614,8 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
 
     `chunk` n: a query sees only the keys of its own run of n positions (runs counted from the request's
     position 0, wherever a prompt was cut); `softcap` c: a scaled score s becomes c tanh(s / c) ahead of
-    the softmax. Both are taken by the generic kernel and by the mma.sync kernels.
+    the softmax. Both are taken by the generic kernel, by the mma.sync kernels and by the tcgen05 prefill
+    kernel that runs two blocks to an SM.
 
     With `projection` (only where `decode_fusable` holds) q is not given: the kernel makes the
     queries and the new keys and values from the projected rows, and writes the latter to the cache.
@@ -639,7 +643,6 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
     run, softcap = int(chunk or 0), float(softcap or 0.0)
     if run and keep:
         raise KernelError("a mask of runs keeps no first positions")
-    tcgen05_ok = not run and not softcap  # the tcgen05 prefill kernels take neither
     if dv != d or not tiled_attention_supported(q.dtype, nq, nkv, d):
         if projection is not None:
             raise KernelError("the generic attention kernel takes queries, not projected rows")
@@ -681,14 +684,16 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
                "attention_decode")
         if step.decode_only or all(n == 1 for n in step.q_lens):
             return out
-    if tcgen05_ok and tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
+    if tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
         per_block = 128 // (nq // nkv)
         sms = sm_count(q.device)
         plain = sink is None and not keep  # a sink or kept first positions: the two-to-an-SM kernel, every block whole
+        narrow = bool(run or softcap)  # runs and capped scores: the two-to-an-SM kernel, blocks cut as ever
         if wide is None:
-            wide = plain and wide_prefill_pays(step.q_lens, step.seq_lens_host, per_block, nkv, kv.window or 0, sms)
-        elif wide and not plain:
-            raise KernelError("the kernel that gives a block its SM takes neither a sink nor kept first positions")
+            wide = plain and not narrow and wide_prefill_pays(step.q_lens, step.seq_lens_host, per_block, nkv,
+                                                              kv.window or 0, sms)
+        elif wide and (not plain or narrow):
+            raise KernelError("the kernel that gives a block its SM takes no sink, kept first positions, runs or cap")
         if wide:
             # Every block whole (no places to share tiles over), an SM to a block.
             work = _prefill_work_flat(step, per_block, 64, nkv, kv.window or 0, q.device, 0)
@@ -699,7 +704,8 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
                       _ptr(work), work.shape[0], gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv,
                       kv.page_size, kv.window or 0, scale, err, _stream()), "attention_prefill_tcgen05_wide")
             return out
-        work = _prefill_work_flat(step, per_block, 64, nkv, kv.window or 0, q.device, prefill_places(sms) if plain else 0)
+        work = _prefill_work_flat(step, per_block, 64, nkv, kv.window or 0, q.device, prefill_places(sms) if plain else 0,
+                                  run)
         # Room for the parts of blocks that are cut (at most one more item per block the device runs at
         # a time) and a ticket per block; the sizes do not depend on the contexts' lengths.
         part_floats = _function("attention_tcgen05", "omnia_attention_tcgen05_part_floats", [], defines)()
@@ -710,10 +716,10 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
         fn = _function("attention_tcgen05", "omnia_attention_prefill_tcgen05",
                        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
-                        c_void_p, c_void_p], defines)
+                        c_int, c_float, c_void_p, c_void_p], defines)
         _check(fn(_ptr(q), tokens, _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens),
                   _ptr(work), work.shape[0], gate_ptr, gate_stride, _ptr(out), _ptr(partial), _ptr(tickets), max_pages,
-                  num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, keep, _ptr(sink), err, _stream()),
+                  num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, keep, _ptr(sink), run, softcap, err, _stream()),
                "attention_prefill_tcgen05")
         return out
     tokens_per_block = 64 // (nq // nkv)

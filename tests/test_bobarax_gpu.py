@@ -141,7 +141,7 @@ def _filled(spec, pages, K, V, page, order):
 
 
 ATTENTION_CASES = [("float32", 4, 2, 16, 24, 4), ("bfloat16", 6, 1, 16, 16, 8), ("bfloat16", 4, 2, 64, 64, 16),
-                   ("bfloat16", 2, 2, 32, 8, 16), ("float32", 4, 1, 24, 24, 16)]
+                   ("bfloat16", 2, 2, 32, 8, 16), ("float32", 4, 1, 24, 24, 16), ("bfloat16", 3, 1, 128, 128, 32)]
 
 
 @pytest.mark.parametrize("dtype,H,G,dk,dv,page", ATTENTION_CASES)
@@ -207,6 +207,43 @@ def test_a_boosted_key_just_inside_and_just_outside(dtype, H, G, dk, dv, page):
             want = _attention_reference(q.to(F64), K, V, step.positions.cpu(), window, chunk, 1.0, None)
             assert rel(got, want) < (2e-5 if dtype == "float32" else 2e-2)
             assert (float(got[row].float().mean()) > 40.0) == inside, (window, chunk, query, key, lens)
+    ops.raise_on_error(CUDA)
+
+
+@pytest.mark.parametrize("H,G,d,run,softcap", [(4, 1, 128, 1024, 20.0), (2, 2, 64, 960, None), (8, 2, 64, 2048, 3.0)])
+def test_long_runs_in_portions_whose_blocks_are_cut_into_parts(H, G, d, run, softcap):
+    """A portion of a prompt deep inside a long run: few blocks, each over many key tiles, which the
+    prefill kernel cuts into parts that are merged by the last to finish. The run's first key is
+    boosted for one query head, so a part that starts a tile late, or a merge that drops the first
+    part, shows; the key just ahead of the run is boosted as much and must not show."""
+    g = torch.Generator().manual_seed(run + d)
+    N, page, dt = 2100, 16, torch.bfloat16
+    K, V = torch.randn(N, G, d, generator=g) * 0.3, torch.randn(N, G, d, generator=g)
+    direction = torch.randn(d, generator=g)
+    direction = direction / direction.norm()
+    start = (N - 1) // run * run  # the last run's first position
+    K[start], V[start] = direction * 8.0, 30.0
+    K[start - 1], V[start - 1] = direction * 8.0, -30.0
+    K, V = K.to(dt).to(F64), V.to(dt).to(F64)
+    spec, pages = _cache(G, d, d, page, -(-N // page) + 2, dt, None, run)
+    order = torch.randperm(pages.shape[0], generator=g).tolist()[: -(-N // page)]
+    kv = _filled(spec, pages, K, V, page, order)
+    for lens, starts in [([90], [N - 90]), ([40, 1, 70], [N - 40, 1500, start - 30])]:
+        step = Batch(lens, starts)
+        q = torch.randn(sum(lens), H, d, generator=g) * 0.3
+        q[:, 0] = direction * 8.0
+        q = q.to(dt)
+        tables = []
+        for n, s in zip(lens, starts):
+            table = list(order[: -(-(s + n) // page)])
+            for index in range(spec.dead_below(s) // page):
+                table[index] = -1
+            tables.append(table)
+        got = ops.paged_attention(q.to(CUDA), _view(spec, pages, tables, page), step, 0.5, chunk=run, softcap=softcap)
+        want = _attention_reference(q.to(F64), K, V, step.positions.cpu(), None, run, 0.5, softcap)
+        assert rel(got, want) < 2e-2, (lens, starts)
+        if not softcap:
+            assert float(got[lens[0] - 1].float().view(H, d)[0].mean()) > 25.0
     ops.raise_on_error(CUDA)
 
 
