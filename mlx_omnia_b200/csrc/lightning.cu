@@ -10,12 +10,14 @@
 // sigmoid gate:  out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate).
 //
 // The recurrence kernel is sequential in a request's tokens and parallel over (request, head, run
-// of value columns): the columns of S are independent. A column is held by P threads, each with
+// of value columns): the columns of S are independent. A column is held by P threads (up to 16), each with
 // DK / P of its rows in registers. The block's other warps are loaders: while the column threads walk
 // one run of LIGHTNING_CHUNK tokens out of shared memory, the loaders fetch the next run's projected
-// rows, apply the activations in float32, round them to the element type, as a product with the
-// activation in its epilogue would store them, and leave them in the other half of a double buffer; the
-// two sides meet at one barrier a run. A token's partial sums stay in registers until its run is done,
+// rows (16 bytes at a time where a head's rows start on 16 bytes and the key width allows), apply the
+// activations in float32, round them to the element type, as a product with the activation in its
+// epilogue would store them, and leave them in the other half of a double buffer; the two sides meet at
+// one barrier a run. A head's q and k are staged once per run of columns, so a block with few columns
+// spends most of its instructions there: what the loaders do per element decides the kernel's pace. A token's partial sums stay in registers until its run is done,
 // so the shuffles that add them up are off the chain from token to token, which is one fused
 // multiply-add a row. The state, the decay and every sum stay float32. It serves decode steps (one
 // token a request) and prompts' portions of any length alike; the order of a column's additions does
@@ -33,7 +35,13 @@
 
 namespace {
 
-__device__ __forceinline__ float silu_f32(float x) { return x / (1.f + expf(-x)); }
+// SiLU in float32. The 16-bit types take the fast exponential and division that the products' fused
+// epilogues take (the result is rounded to 8 bits of mantissa next), float32 the exact ones.
+template <typename T>
+__device__ __forceinline__ float silu_as(float x) {
+  if constexpr (sizeof(T) == 2) return __fdividef(x, 1.f + __expf(-x));
+  else return x / (1.f + expf(-x));
+}
 
 template <typename T, int P>
 __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel(
@@ -44,10 +52,16 @@ __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel
   pdl_launch_dependents();
   constexpr int DK = LIGHTNING_DK;
   constexpr int R = (DK + P - 1) / P;
-  constexpr int SEG = R + 1;     // a thread's rows, padded so that the P segments fall on different banks
+  // A thread's rows sit in a segment of their own, padded so that the P segments fall on different
+  // banks: by four floats when the rows come in fours (segments then start on 16 bytes and are read
+  // and written four floats at a time), else by one.
+  constexpr bool FOURS = R % 4 == 0;
+  constexpr int SEG = FOURS ? R + 4 : R + 1;
   constexpr int VROW = P * SEG;  // floats of one token's vector of DK
   constexpr int TC = LIGHTNING_CHUNK;
-  extern __shared__ float shared[];
+  constexpr int VEC = 16 / (int)sizeof(T);  // elements in 16 bytes of a projected row
+  constexpr bool EXACT = P * R == DK;       // every thread's R rows are rows of S: nothing to guard
+  extern __shared__ __align__(16) float shared[];
   const int half = 2 * TC * VROW + TC * cols;  // floats of one buffer: q [TC][VROW] | k [TC][VROW] | v [TC][cols]
   const int head = blockIdx.x / parts, part = blockIdx.x % parts, seq = blockIdx.y;
   const int col0 = part * cols;
@@ -58,8 +72,72 @@ __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel
   const int j = threadIdx.x / P, p = threadIdx.x % P;
   const bool live = !loader && j < cols && col0 + j < dv;
   const float lambda = decay[head];
+  // Whether this block's q, k and v can be fetched 16 bytes at a time: whole pieces, every row's start on 16 bytes.
+  const bool wide = FOURS && DK % VEC == 0 && cols % VEC == 0 && (stride * sizeof(T)) % 16 == 0 &&
+                    (reinterpret_cast<uintptr_t>(proj + q_col + head * DK) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(proj + k_col + head * DK) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(proj + v_col + head * dv + col0) & 15) == 0;
+  constexpr int PIECES = DK / VEC > 0 ? DK / VEC : 1;  // 16-byte pieces of a head's q (and k) row
+  const int v_pieces = cols / VEC, per_token = 2 * PIECES + v_pieces;
+  uint4* raw = reinterpret_cast<uint4*>(shared + 2 * half);  // [TC * per_token] pieces as they come from memory
 
-  // Tokens [t0, t0 + n) into buffer `buf`: activations in float32, rounded to the element type.
+  // The wide way has two steps a run. `fetch` starts the copies of tokens [t0, t0 + n) into `raw`
+  // (asynchronous copies: the thread goes on at once); `cook` waits for this thread's own copies, applies
+  // the activations in float32, rounds to the element type and lays the floats out for the column
+  // threads. A thread cooks exactly the pieces it fetched, so the loaders need no barrier of their own,
+  // and the copies of one run are in flight while the run before it is walked.
+  auto fetch = [&](int t0, int n) {
+    for (int item = lt; item < n * per_token; item += loaders) {
+      const int tok = item / per_token, r = item % per_token;
+      const T* row = proj + (size_t)(t0 + tok) * stride;
+      const T* src = r < PIECES       ? row + q_col + head * DK + r * VEC
+                     : r < 2 * PIECES ? row + k_col + head * DK + (r - PIECES) * VEC
+                                      : row + v_col + head * dv + col0 + (r - 2 * PIECES) * VEC;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(raw + item)), "l"(src)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto cook = [&](int n, float* buf) {
+    float* qs = buf;
+    float* ks = buf + TC * VROW;
+    float* vs = ks + TC * VROW;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    for (int item = lt; item < n * per_token; item += loaders) {
+      const int tok = item / per_token, r = item % per_token;
+      const uint4 piece = raw[item];
+      float x[VEC];
+      if constexpr (sizeof(T) == 4) {
+        x[0] = __uint_as_float(piece.x), x[1] = __uint_as_float(piece.y), x[2] = __uint_as_float(piece.z),
+        x[3] = __uint_as_float(piece.w);
+      } else {
+        const T* e = reinterpret_cast<const T*>(&piece);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) x[i] = to_f32(e[i]);
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) x[e] = to_f32(from_f32<T>(silu_as<T>(x[e])));
+      float* dst;
+      if (r < 2 * PIECES) {
+        const int i0 = (r < PIECES ? r : r - PIECES) * VEC;
+        dst = (r < PIECES ? qs : ks) + tok * VROW + (i0 / R) * SEG + i0 % R;  // VEC divides R or R divides VEC's fours
+        if constexpr (VEC == 8 && R % 8 != 0) {
+          // The second four floats may belong to the next segment.
+          const int i1 = i0 + 4;
+          *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);
+          dst = (r < PIECES ? qs : ks) + tok * VROW + (i1 / R) * SEG + i1 % R;
+          *reinterpret_cast<float4*>(dst) = make_float4(x[4], x[5], x[6], x[7]);
+          continue;
+        }
+      } else {
+        dst = vs + tok * cols + (r - 2 * PIECES) * VEC;
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(x[e], x[e + 1], x[e + 2], x[e + 3]);
+    }
+  };
+
+  // The plain way: tokens [t0, t0 + n) into buffer `buf`, element by element.
   auto stage = [&](int t0, int n, float* buf) {
     float* qs = buf;
     float* ks = buf + TC * VROW;
@@ -70,14 +148,14 @@ __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel
       const T* src = proj + (size_t)(t0 + tok) * stride + head * DK + i;
       const float q = to_f32(src[q_col]), k = to_f32(src[k_col]);
       const int at = tok * VROW + (i / R) * SEG + i % R;
-      qs[at] = to_f32(from_f32<T>(silu_f32(q)));
-      ks[at] = to_f32(from_f32<T>(silu_f32(k)));
+      qs[at] = to_f32(from_f32<T>(silu_as<T>(q)));
+      ks[at] = to_f32(from_f32<T>(silu_as<T>(k)));
     }
 #pragma unroll 4
     for (int idx = lt; idx < n * cols; idx += loaders) {
       const int tok = idx / cols, c = idx % cols;
       vs[idx] = col0 + c < dv
-                    ? to_f32(from_f32<T>(silu_f32(to_f32(proj[(size_t)(t0 + tok) * stride + v_col + head * dv + col0 + c]))))
+                    ? to_f32(from_f32<T>(silu_as<T>(to_f32(proj[(size_t)(t0 + tok) * stride + v_col + head * dv + col0 + c]))))
                     : 0.f;
     }
   };
@@ -91,13 +169,28 @@ __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel
   }
 
   const int runs = (end - begin + TC - 1) / TC;
-  if (loader) stage(begin, min(TC, end - begin), shared);
+  if (loader) {
+    if (wide) {
+      fetch(begin, min(TC, end - begin));
+      cook(min(TC, end - begin), shared);
+      if (runs > 1) fetch(begin + TC, min(TC, end - begin - TC));
+    } else {
+      stage(begin, min(TC, end - begin), shared);
+    }
+  }
   __syncthreads();
   for (int c = 0; c < runs; ++c) {
     const int t0 = begin + c * TC;
     const int n = min(TC, end - t0);
     if (loader) {
-      if (c + 1 < runs) stage(t0 + TC, min(TC, end - t0 - TC), shared + ((c + 1) & 1) * half);
+      if (c + 1 < runs) {
+        if (wide) {
+          cook(min(TC, end - t0 - TC), shared + ((c + 1) & 1) * half);
+          if (c + 2 < runs) fetch(t0 + 2 * TC, min(TC, end - t0 - 2 * TC));
+        } else {
+          stage(t0 + TC, min(TC, end - t0 - TC), shared + ((c + 1) & 1) * half);
+        }
+      }
     } else {
       const float* qs = shared + (c & 1) * half;
       const float* ks = qs + TC * VROW;
@@ -110,14 +203,29 @@ __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel
           const float* kt = ks + tok * VROW + p * SEG;
           const float* qt = qs + tok * VROW + p * SEG;
           const float v = live ? vs[tok * cols + j] : 0.f;
-          float o = 0.f;
+          // Four partial sums, so that a token's dot product is four short chains instead of one of R.
+          float o[4] = {0.f, 0.f, 0.f, 0.f};
+          if constexpr (FOURS) {
 #pragma unroll
-          for (int i = 0; i < R; ++i)
-            if (p * R + i < DK) {
-              S[i] = fmaf(kt[i], v, lambda * S[i]);
-              o = fmaf(S[i], qt[i], o);
+            for (int i = 0; i < R; i += 4) {
+              const float4 k4 = *reinterpret_cast<const float4*>(kt + i), q4 = *reinterpret_cast<const float4*>(qt + i);
+              const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (EXACT || p * R + i + e < DK) {
+                  S[i + e] = fmaf(kk[e], v, lambda * S[i + e]);
+                  o[e] = fmaf(S[i + e], qq[e], o[e]);
+                }
             }
-          sums[tok] = o;
+          } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+              if (EXACT || p * R + i < DK) {
+                S[i] = fmaf(kt[i], v, lambda * S[i]);
+                o[i & 3] = fmaf(S[i], qt[i], o[i & 3]);
+              }
+          }
+          sums[tok] = (o[0] + o[1]) + (o[2] + o[3]);
         }
       }
 #pragma unroll
@@ -176,7 +284,8 @@ extern "C" int omnia_lightning_recurrence(const void* proj, int stride, int q_co
 #define OMNIA_LIGHTNING_LAUNCH(P)                                                                              \
   do {                                                                                                         \
     constexpr int R = (LIGHTNING_DK + P - 1) / P;                                                              \
-    const size_t smem = sizeof(float) * 2 * ((size_t)2 * LIGHTNING_CHUNK * P * (R + 1) + LIGHTNING_CHUNK * cols); \
+    const size_t smem = sizeof(float) * 2 * ((size_t)2 * LIGHTNING_CHUNK * P * (R % 4 == 0 ? R + 4 : R + 1) + LIGHTNING_CHUNK * cols) + \
+                        (size_t)LIGHTNING_CHUNK * (2 * (LIGHTNING_DK * sizeof(T) / 16 + 1) + cols * sizeof(T) / 16 + 1) * 16; \
     if (smem > 48 * 1024 && cudaFuncSetAttribute(lightning_recurrence_kernel<T, P>,                            \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
       return (int)cudaGetLastError();                                                                          \
@@ -185,9 +294,14 @@ extern "C" int omnia_lightning_recurrence(const void* proj, int stride, int q_co
                (const T*)proj, stride, q_col, k_col, v_col, H, dv, cols, parts, column_threads, decay, S_state, \
                cu_seqlens, state_slots, o_raw);                                                                \
   } while (0)
+  // Threads a column: as many as leave each at least four rows of S and fit the block. A column's
+  // threads share out its rows, so more of them shorten what a token costs a warp; their partial sums
+  // meet in shuffles after a run of tokens, off the chain from token to token.
   constexpr int ROOM = LIGHTNING_THREADS - LIGHTNING_LOADERS;  // threads left for the columns
   OMNIA_DISPATCH_DTYPE(dtype, {
-    if (cols * 4 <= ROOM && LIGHTNING_DK >= 16) OMNIA_LIGHTNING_LAUNCH(4);
+    if (cols * 16 <= ROOM && LIGHTNING_DK >= 64) OMNIA_LIGHTNING_LAUNCH(16);
+    else if (cols * 8 <= ROOM && LIGHTNING_DK >= 32) OMNIA_LIGHTNING_LAUNCH(8);
+    else if (cols * 4 <= ROOM && LIGHTNING_DK >= 16) OMNIA_LIGHTNING_LAUNCH(4);
     else if (cols * 2 <= ROOM && LIGHTNING_DK >= 8) OMNIA_LIGHTNING_LAUNCH(2);
     else if (cols <= ROOM) OMNIA_LIGHTNING_LAUNCH(1);
     else return (int)cudaErrorInvalidValue;

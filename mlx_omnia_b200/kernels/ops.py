@@ -1266,20 +1266,22 @@ def lightning_parts(requests: int, heads: int, dv: int, sms: int) -> int:
     """Into how many runs of columns the recurrence kernel cuts a head's value channels: at least as
     many as bring a run down to 96 columns (four threads a column then fit a block; 192 and 384 where
     dv divides no better), and beyond that the fewest equal runs (of at least 8 columns) that give
-    every SM a block when (request, head) pairs alone do not."""
+    three quarters of the SMs a block when (request, head) pairs alone do not: every block stages its
+    head's q and k for itself, so twice the blocks for the last quarter of the SMs is twice that work."""
     divisors = [parts for parts in range(1, dv + 1) if dv % parts == 0]
     least = next((parts for limit in (96, 192, 384) for parts in divisors if 8 <= dv // parts <= limit or
                   (dv // parts <= limit and parts == 1)), None)
     if least is None:
         least = next(parts for parts in divisors if dv // parts <= 96)
     blocks = requests * heads
+    enough = sms - sms // 4
     best = least
-    if blocks < sms:
+    if blocks < enough:
         for parts in divisors:
             if parts < least or dv // parts < 8:
                 continue
             best = parts
-            if blocks * parts >= sms:
+            if blocks * parts >= enough:
                 break
     return best
 
