@@ -176,3 +176,46 @@ def test_which_tcgen05_kernel_takes_gate_up_with_swiglu():
     assert not pair(200)                            # under a pair's 256 rows
     assert not pair(896, 24576)                     # twice the columns: five waves of SMs against six of pairs
     assert ops.FUSED_GATE_ROWS <= 384
+
+
+def test_prefill_work_table_counts_a_block_from_the_run_of_its_first_row():
+    """With runs, a block's key tiles begin at the run that holds its first token (rows of a later
+    run mask the rest), so the parts of a cut block cover exactly those tiles."""
+    run, tile, per_block, nkv = 1024, 64, 32, 2
+    table = ops.prefill_work_table([90], [2100], per_block, tile, nkv, 0, 222, run=run)
+    covered = {}
+    for s, t0, h, lo, count, packed, slot0, unit in table.tolist():
+        parts, part = packed & 255, packed >> 8
+        pos0 = 2100 - 90 + t0
+        last = pos0 + min(per_block, 90 - t0) - 1
+        first = pos0 - pos0 % run
+        tiles = last // tile - first // tile + 1
+        covered.setdefault((t0, h), []).append((lo, tiles if count < 0 else count, parts, part))
+        assert count < 0 or 0 < count <= tiles
+    assert len(covered) == 3 * nkv
+    for (t0, h), pieces in covered.items():
+        pos0 = 2100 - 90 + t0
+        tiles = (pos0 + min(per_block, 90 - t0) - 1) // tile - (pos0 - pos0 % run) // tile + 1
+        pieces.sort()
+        assert [p[3] for p in pieces] == list(range(pieces[0][2]))
+        assert pieces[0][0] == 0 and sum(p[1] for p in pieces) == tiles
+        assert all(a[0] + a[1] == b[0] for a, b in zip(pieces, pieces[1:]))
+    # The block that starts in the earlier run walks its tiles too; the one inside the last run only its own.
+    assert sum(p[1] for p in covered[(0, 0)]) == 2099 // tile - 1024 // tile + 1 - (2099 // tile - 2041 // tile)
+    assert sum(p[1] for p in covered[(64, 0)]) == 2099 // tile - 2048 // tile + 1
+    # A window and a run together: the later of the two starts.
+    both = ops.prefill_work_table([40], [3000], 64, tile, 1, 100, 0, run=2048)
+    assert both.tolist()[0][4] == -1 and both.shape[0] == 1
+
+
+def test_lightning_parts_divide_the_columns_and_fit_a_block():
+    for requests in (1, 2, 8, 64):
+        for heads in (1, 3, 16, 32):
+            for dv in (7, 8, 16, 20, 24, 64, 96, 128, 192, 256):
+                parts = ops.lightning_parts(requests, heads, dv, 148)
+                cols = dv // parts
+                assert dv % parts == 0 and 1 <= cols <= 384
+                assert cols >= 8 or parts == 1 or dv // 8 == 0
+    # One prompt of 16 heads: blocks for three quarters of the SMs, not two blocks an SM for the rest.
+    assert ops.lightning_parts(1, 16, 128, 148) == 8
+    assert ops.lightning_parts(64, 16, 128, 148) == 2
