@@ -727,6 +727,29 @@ extern "C" int omnia_activation(const void* z, void* act, long long total, int k
 }
 
 // ---------------------------------------------------------------------------------
+// out = sa * a + sb * b, the sum taken in float32 and rounded once: two branches that read the same
+// input meet with a constant each.
+template <typename T>
+__global__ void scaled_sum_kernel(const T* __restrict__ a, float sa, const T* __restrict__ b, float sb, T* __restrict__ out,
+                                  long long total) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride)
+    out[idx] = from_f32<T>(fmaf(sa, to_f32(a[idx]), sb * to_f32(b[idx])));
+}
+
+extern "C" int omnia_scaled_sum(const void* a, float sa, const void* b, float sb, void* out, long long total, int dtype,
+                                cudaStream_t stream) {
+  if (total == 0) return 0;
+  const long long most = 16LL * omnia_sm_count();
+  const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(scaled_sum_kernel<T>, blocks, 256, 0, stream, (const T*)a, sa, (const T*)b, sb,
+                                          (T*)out, total)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
 // logits = cap * tanh(z * multiplier / cap)  (cap <= 0: logits = z * multiplier), float32 out.
 template <typename T>
 __global__ void softcap_kernel(const T* __restrict__ z, float* __restrict__ out, long long total,

@@ -42,8 +42,8 @@ __device__ __forceinline__ float gated_unit(float gate, float up, float alpha, f
 template <typename T, int TOK, int THREADS, int CHUNK>
 __global__ void __launch_bounds__(THREADS)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
-                 int tokens, int outputs, int experts, int hidden, int top, int* __restrict__ choice,
-                 float* __restrict__ weight, int* __restrict__ counts) {
+                 int tokens, int outputs, int experts, int hidden, int top, int sigmoid_scores,
+                 int* __restrict__ choice, float* __restrict__ weight, int* __restrict__ counts) {
   pdl_wait();
   pdl_launch_dependents();
   constexpr int WARPS = THREADS / 32;
@@ -119,7 +119,8 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
   for (int e = lane; e < outputs; e += 32) sum += expf(score[e] - top_z);
   sum = warp_sum(sum);
   for (int e = lane; e < outputs; e += 32) {
-    const float s = expf(score[e] - top_z) / sum;
+    // Every output's score by itself (a sigmoid), or its share among all outputs (a softmax).
+    const float s = sigmoid_scores ? 1.f / (1.f + expf(-score[e])) : expf(score[e] - top_z) / sum;
     score[e] = s;
     pick[e] = s + (correction ? correction[e] : 0.f);
   }
@@ -447,10 +448,13 @@ moe_product_tc_kernel(const bf16* __restrict__ a, const int* __restrict__ source
 
 // ---------------------------------------------------------------------------------
 // y[t] = sum over the token's choices, in their order, of weight * (the choice's row of `rows`, or the
-// token's own input h[t] for an identity expert). One block per token.
+// token's own input h[t] for an identity expert), plus row t of `extra` when given (an expert that every
+// token uses). No `weight`: every choice counts once (the weights went into the experts' inputs). One
+// block per token.
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ rows, const T* __restrict__ h, const int* __restrict__ place,
-                                   const float* __restrict__ weight, T* __restrict__ y, int hidden, int top) {
+                                   const float* __restrict__ weight, const T* __restrict__ extra, T* __restrict__ y,
+                                   int hidden, int top) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -459,30 +463,32 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const T* __restri
     for (int k = 0; k < top; ++k) {
       const int p = place[(size_t)t * top + k];
       const float v = p >= 0 ? to_f32(rows[(size_t)p * hidden + i]) : to_f32(h[(size_t)t * hidden + i]);
-      acc += weight[(size_t)t * top + k] * v;
+      acc += weight ? weight[(size_t)t * top + k] * v : v;
     }
+    if (extra) acc += to_f32(extra[(size_t)t * hidden + i]);
     y[(size_t)t * hidden + i] = from_f32<T>(acc);
   }
 }
 
 template <typename T, int TOK, int THREADS, int CHUNK>
 int launch_route(const T* h, const float* router, const float* correction, int tokens, int outputs, int experts,
-                 int hidden, int top, int* choice, float* weight, int* counts, size_t smem, cudaStream_t stream) {
+                 int hidden, int top, int sigmoid_scores, int* choice, float* weight, int* counts, size_t smem,
+                 cudaStream_t stream) {
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<T, TOK, THREADS, CHUNK>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   launch_pdl(moe_route_kernel<T, TOK, THREADS, CHUNK>, (tokens + TOK - 1) / TOK, THREADS, smem, stream, h, router, correction, tokens,
-             outputs, experts, hidden, top, choice, weight, counts);
+             outputs, experts, hidden, top, sigmoid_scores, choice, weight, counts);
   return OMNIA_LAUNCH_RESULT();
 }
 
 }  // namespace
 
 extern "C" int omnia_moe_route(const void* h, const float* router, const float* correction, int tokens, int outputs,
-                               int experts, int hidden, int top, int* choice, float* weight, int* counts, int dtype,
-                               cudaStream_t stream) {
+                               int experts, int hidden, int top, int sigmoid_scores, int* choice, float* weight,
+                               int* counts, int dtype, cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (top < 1 || top > outputs || experts < 0 || experts > outputs || outputs > 4096) return (int)cudaErrorInvalidValue;
   const int padded = (outputs + 3) / 4 * 4;
@@ -492,10 +498,10 @@ extern "C" int omnia_moe_route(const void* h, const float* router, const float* 
   if (bytes(1) > 200 * 1024) return (int)cudaErrorInvalidValue;
   OMNIA_DISPATCH_DTYPE(dtype, {
     if (many)
-      return launch_route<T, 8, 256, 4>((const T*)h, router, correction, tokens, outputs, experts, hidden, top, choice, weight,
-                                counts, bytes(8), stream);
-    return launch_route<T, 1, 1024, 1>((const T*)h, router, correction, tokens, outputs, experts, hidden, top, choice, weight,
-                              counts, bytes(1), stream);
+      return launch_route<T, 8, 256, 4>((const T*)h, router, correction, tokens, outputs, experts, hidden, top,
+                                        sigmoid_scores, choice, weight, counts, bytes(8), stream);
+    return launch_route<T, 1, 1024, 1>((const T*)h, router, correction, tokens, outputs, experts, hidden, top,
+                                       sigmoid_scores, choice, weight, counts, bytes(1), stream);
   });
   return (int)cudaErrorInvalidValue;
 }
@@ -612,6 +618,32 @@ __global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict
   }
 }
 
+// rows[place[t * top + k]] = weight[t * top + k] * h[t]: the sorted order made contiguous with every
+// row multiplied by its choice's weight (float32 product, rounded once), for experts that are given
+// the weighted token instead of having their output weighed. Choices without a place (identity
+// experts) are passed over. One block per (token, choice).
+template <typename T>
+__global__ void moe_weighted_rows_kernel(const T* __restrict__ h, const int* __restrict__ place,
+                                         const float* __restrict__ weight, T* __restrict__ rows, int hidden, int top) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int pair = blockIdx.x;
+  const int r = place[pair];
+  if (r < 0) return;
+  const float w = weight[pair];
+  const T* src = h + (size_t)(pair / top) * hidden;
+  T* dst = rows + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>(w * to_f32(src[i]));
+}
+
+extern "C" int omnia_moe_weighted_rows(const void* h, const int* place, const float* weight, void* rows, int pairs,
+                                       int hidden, int top, int dtype, cudaStream_t stream) {
+  if (pairs == 0) return 0;
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(moe_weighted_rows_kernel<T>, pairs, 128, 0, stream, (const T*)h, place, weight,
+                                          (T*)rows, hidden, top)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
 extern "C" int omnia_moe_gather(const void* h, const int* source, const int* total, void* rows, int pairs, int hidden,
                                 int dtype, cudaStream_t stream) {
   if (pairs == 0) return 0;
@@ -620,10 +652,10 @@ extern "C" int omnia_moe_gather(const void* h, const int* source, const int* tot
   return OMNIA_LAUNCH_RESULT();
 }
 
-extern "C" int omnia_moe_combine(const void* rows, const void* h, const int* place, const float* weight, void* y,
-                                 int tokens, int hidden, int top, int dtype, cudaStream_t stream) {
+extern "C" int omnia_moe_combine(const void* rows, const void* h, const int* place, const float* weight, const void* extra,
+                                 void* y, int tokens, int hidden, int top, int dtype, cudaStream_t stream) {
   if (tokens == 0) return 0;
   OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(moe_combine_kernel<T>, tokens, 256, 0, stream, (const T*)rows, (const T*)h,
-                                          place, weight, (T*)y, hidden, top)));
+                                          place, weight, (const T*)extra, (T*)y, hidden, top)));
   return OMNIA_LAUNCH_RESULT();
 }

@@ -1314,6 +1314,140 @@ def lightning_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, 
     return out
 
 
+def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float) -> torch.Tensor:
+    """sa * a + sb * b, element by element, the sum in float32 and rounded once."""
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise KernelError("scaled_sum takes two tensors of one shape and type")
+    out = torch.empty_like(a)
+    fn = _function("elementwise", "omnia_scaled_sum",
+                   [c_void_p, c_float, c_void_p, c_float, c_void_p, c_longlong, c_int, c_void_p])
+    _check(fn(_ptr(a), sa, _ptr(b), sb, _ptr(out), a.numel(), _code(a.dtype), _stream()), "scaled_sum")
+    return out
+
+
+# ------------------------------------------------------------------------------------
+# Linear attention with a decay per head or per key channel (csrc/state_recurrence.cu)
+
+
+def state_columns(requests: int, heads: int, dk: int, dv: int, sms: int) -> int:
+    """How many of a head's value columns a block of the recurrence kernel takes: at most 96 (four
+    threads a column then fit a block) and no more than the key width leaves room for (a column needs
+    enough threads that each holds at most 32 rows of the state); in fours where dv comes in fours; and
+    halved, down to 16, while (request, head, run of columns) triples leave a quarter of the SMs idle."""
+    threads = 1
+    while -(-dk // threads) > 32:
+        threads *= 2
+    most = min(96, 512 // threads)
+    cols = min(dv, most)
+    if dv % 4 == 0:
+        cols = max(4, cols // 4 * 4)
+    while cols >= 32 and requests * heads * -(-dv // cols) < sms - sms // 4:
+        cols = -(-cols // 2)
+        if dv % 4 == 0:
+            cols = -(-cols // 4) * 4
+    return cols
+
+
+def state_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gate_col: int, heads: int, dk: int, dv: int,
+                    S: torch.Tensor, step: StepContext, eps: float, decay: torch.Tensor | None = None,
+                    decay_logits: torch.Tensor | None = None, decay_bias: torch.Tensor | None = None, tau: float = 1.0,
+                    inv_freq: torch.Tensor | None = None, q_scale: float = 1.0, k_scale: float = 1.0,
+                    norm_weight: torch.Tensor | None = None, gate: str = "silu",
+                    cols: int | None = None) -> torch.Tensor:
+    """Linear attention over this step's tokens, request by request from the state in `S`
+    [slots, heads, dk, dv] (float32, updated in place): per head S <- diag(a) S + k v^T, o = S^T q.
+    q, k (heads * dk each) and v (heads * dv) are columns of the projected rows `proj`; q and k are
+    turned over the first 2 * len(inv_freq) dims of every head in half-split pairs (float32 angles from
+    the step's positions) and then multiplied by q_scale and k_scale, all in float32, and enter the
+    recurrence unrounded. The decay is `decay` (float32 [heads], a constant a head) or, with
+    `decay_logits` [tokens, heads * dk], a = sigmoid(logits + decay_bias)^(1 / tau) per token and key
+    channel. Every head's o is divided by its own root mean square (`eps` inside the root), multiplied
+    by `norm_weight` ([dv], shared by the heads; None: no weight) and by silu or sigmoid (`gate`) of the
+    columns from gate_col. `cols`: value columns a block takes. -> [tokens, heads * dv]"""
+    tokens, stride = proj.shape
+    if (decay is None) == (decay_logits is None):
+        raise KernelError("state_attention takes either a decay per head or decay logits per token")
+    if gate not in ("silu", "sigmoid"):
+        raise KernelError(f"state_attention gates by silu or sigmoid, not {gate!r}")
+    channel = decay_logits is not None
+    defines = {"STATE_DK": dk}
+    width = heads * dv
+    if cols is None:
+        cols = state_columns(step.num_seqs, heads, dk, dv, sm_count(proj.device))
+    row_floats = 2 * (-(-heads * dk // 4) * 4) + -(-width // 4) * 4 + (-(-heads * dk // 4) * 4 if channel else 0)
+    rows = torch.empty(tokens, row_floats, dtype=torch.float32, device=proj.device)
+    rot = 0 if inv_freq is None else 2 * inv_freq.shape[0]
+    fn = _function("state_recurrence", "omnia_state_inputs",
+                   [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
+                    c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p], defines)
+    _check(fn(_ptr(proj), stride, q_col, k_col, v_col, heads, dv, _ptr(inv_freq), rot, _ptr(step.positions), q_scale,
+              k_scale, _ptr(decay_logits), decay_logits.stride(0) if channel else 0, _ptr(decay_bias), 1.0 / tau, _ptr(rows),
+              tokens, _code(proj.dtype), _stream()), "state_inputs")
+    o_raw = torch.empty(tokens, width, dtype=torch.float32, device=proj.device)
+    fn = _function("state_recurrence", "omnia_state_recurrence",
+                   [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                    c_void_p], defines)
+    _check(fn(_ptr(rows), heads, dv, cols, int(channel), _ptr(decay), _ptr(S), _ptr(step.cu_seqlens),
+              _ptr(step.state_slots), step.num_seqs, _ptr(o_raw), _stream()), "state_recurrence")
+    out = torch.empty(tokens, width, dtype=proj.dtype, device=proj.device)
+    fn = _function("state_recurrence", "omnia_state_heads_out",
+                   [c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+                   defines)
+    _check(fn(_ptr(o_raw), proj.data_ptr() + gate_col * proj.element_size(), stride, _ptr(norm_weight), eps, heads, dv,
+              tokens, int(gate == "silu"), _ptr(out), _code(proj.dtype), _stream()), "state_heads_out")
+    return out
+
+
+# ------------------------------------------------------------------------------------
+# A real-gated linear recurrence over channels behind a short convolution (csrc/rglru.cu)
+
+RGLRU_MAX_TAPS = 16
+RGLRU_SCAN_WARPS = 16
+
+
+def gated_channel_recurrence(proj: torch.Tensor, x_col: int, y_col: int, x_bias: torch.Tensor | None,
+                             y_bias: torch.Tensor | None, taps: torch.Tensor, conv_bias: torch.Tensor | None,
+                             gates: torch.Tensor, r_bias: torch.Tensor, i_bias: torch.Tensor, lam: torch.Tensor,
+                             c_decay: float, S: torch.Tensor, conv_state: torch.Tensor, step: StepContext,
+                             warps: int | None = None) -> torch.Tensor:
+    """The recurrence S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t over `channels` independent channels,
+    request by request from `S` [slots, channels] (float32, updated in place), with
+    u = a causal convolution (`taps` [channels, K], the last column the current token's; `conv_bias`) of
+    x = proj[:, x_col:] + x_bias continued from `conv_state` [slots, K - 1, channels] (the request's last
+    inputs, moved on); r, i = sigmoid of block-diagonal maps of u (`gates` float32 [blocks, width,
+    2 * width]: r's columns, then i's; a batched vendor product in true float32) plus `r_bias`, `i_bias`;
+    a = exp(-c_decay * r * softplus(lam)). Everything from x on is float32.
+    -> S_t * gelu_tanh(proj[:, y_col:] + y_bias) as [tokens, channels] in proj's type."""
+    tokens, stride = proj.shape
+    C, K = taps.shape
+    blocks, bw = gates.shape[0], gates.shape[1]
+    if blocks * bw != C or gates.shape[2] != 2 * bw or not 1 <= K <= RGLRU_MAX_TAPS:
+        raise KernelError(f"a recurrence over {C} channels in {blocks} blocks of {bw}, {K} taps")
+    device, code = proj.device, _code(proj.dtype)
+    u = torch.empty(tokens, C, dtype=torch.float32, device=device)
+    fn = _function("rglru", "omnia_rglru_conv",
+                   [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                    c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(proj), stride, x_col, _ptr(x_bias), _ptr(taps), _ptr(conv_bias), C, K, _ptr(conv_state),
+              _ptr(step.cu_seqlens), _ptr(step.state_slots), step.num_seqs, _ptr(u), tokens, code, _stream()), "rglru_conv")
+    z = batched_mm(u.view(tokens, blocks, bw).transpose(0, 1), gates)  # [blocks, tokens, 2 bw]
+    a, b, y = (torch.empty(tokens, C, dtype=torch.float32, device=device) for _ in range(3))
+    fn = _function("rglru", "omnia_rglru_gates",
+                   [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                    c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(u), _ptr(z), _ptr(r_bias), _ptr(i_bias), _ptr(lam), c_decay, _ptr(proj), stride, y_col, _ptr(y_bias), C,
+              bw, tokens, _ptr(a), _ptr(b), _ptr(y), code, _stream()), "rglru_gates")
+    if warps is None:
+        warps = max(1, min(RGLRU_SCAN_WARPS, step.max_q_len // 32))
+    out = torch.empty(tokens, C, dtype=proj.dtype, device=device)
+    fn = _function("rglru", "omnia_rglru_scan",
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                    c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(a), _ptr(b), _ptr(y), C, K, _ptr(S), _ptr(conv_state), _ptr(proj), stride, x_col, _ptr(x_bias),
+              _ptr(step.cu_seqlens), _ptr(step.state_slots), step.num_seqs, warps, _ptr(out), code, _stream()), "rglru_scan")
+    return out
+
+
 # ------------------------------------------------------------------------------------
 # Attention over a latent cache (csrc/attention_latent.cu)
 
@@ -1425,19 +1559,22 @@ def batched_mm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, experts: int, top: int,
-              counts: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+              counts: torch.Tensor, scoring: str = "softmax") -> tuple[torch.Tensor, torch.Tensor]:
     """Per row of `h`: float32 logits against `router` (float32 [outputs, hidden]), softmax over all
-    outputs, the `top` largest of score + correction; -> (choice int32 [rows, top], weight float32
+    outputs (or, with `scoring` "sigmoid", every output's own sigmoid), the `top` largest of score +
+    correction; -> (choice int32 [rows, top], weight float32
     [rows, top]: the chosen outputs' scores, not renormalised). Outputs at or beyond `experts` are identity experts; the
     others are counted into `counts` (int32 [experts], zero before the call)."""
     rows, hidden = h.shape
     choice = torch.empty(rows, top, dtype=torch.int32, device=h.device)
     weight = torch.empty(rows, top, dtype=torch.float32, device=h.device)
+    if scoring not in ("softmax", "sigmoid"):
+        raise KernelError(f"router scores are a softmax or sigmoids, not {scoring!r}")
     fn = _function("moe", "omnia_moe_route",
-                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                    c_void_p])
-    _check(fn(_ptr(h), _ptr(router), _ptr(correction), rows, router.shape[0], experts, hidden, top, _ptr(choice),
-              _ptr(weight), _ptr(counts), _code(h.dtype), _stream()), "moe_route")
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                    c_int, c_void_p])
+    _check(fn(_ptr(h), _ptr(router), _ptr(correction), rows, router.shape[0], experts, hidden, top,
+              int(scoring == "sigmoid"), _ptr(choice), _ptr(weight), _ptr(counts), _code(h.dtype), _stream()), "moe_route")
     return choice, weight
 
 
@@ -1469,7 +1606,8 @@ def moe_experts(h: torch.Tensor, router: torch.Tensor | None, correction: torch.
                 down: torch.Tensor, top: int, step: StepContext | None = None,
                 tensor_cores: bool | None = None, tcgen05: bool | None = None,
                 table: torch.Tensor | None = None, token_ids: torch.Tensor | None = None,
-                alpha: float = 1.0, limit: float = 0.0) -> torch.Tensor:
+                alpha: float = 1.0, limit: float = 0.0, scoring: str = "softmax", weigh: str = "output",
+                extra: torch.Tensor | None = None) -> torch.Tensor:
     """A routed mixture of gated feed-forward experts over the rows of `h` [rows, hidden]:
     y = sum over a row's `top` choices of score * expert(h), expert e being
     down[e] (silu(gate_e h) * (up_e h)) with gate_up [experts, 2 inner, hidden] (gate rows, then up
@@ -1481,7 +1619,13 @@ def moe_experts(h: torch.Tensor, router: torch.Tensor | None, correction: torch.
 
     With `table` (int32 [vocab, top]) and the rows' `token_ids` there is no router: a token's experts are
     its id's row of the table, each weighing 1 / top. `limit` > 0 makes every expert the clamped unit
-    g = min(gate h, limit), u = clamp(up h, -limit, limit), down(g sigmoid(alpha g) (u + 1))."""
+    g = min(gate h, limit), u = clamp(up h, -limit, limit), down(g sigmoid(alpha g) (u + 1)).
+    `scoring`: the router's scores are a "softmax" over all outputs or every output's own "sigmoid".
+    `weigh` "input": y = sum of expert(score * h) instead: a choice's score multiplies what its expert
+    is given (the product in float32, rounded once), and the experts' outputs are added as they are.
+    `extra` [rows, hidden]: added to y in the same pass (an expert that every row uses)."""
+    if weigh not in ("output", "input"):
+        raise KernelError(f"a choice's weight goes on its expert's output or input, not {weigh!r}")
     rows, hidden = h.shape
     experts, inner = gate_up.shape[0], gate_up.shape[1] // 2
     pairs = rows * top
@@ -1499,7 +1643,7 @@ def moe_experts(h: torch.Tensor, router: torch.Tensor | None, correction: torch.
     if table is not None:
         choice, weight = moe_route_table(token_ids[:rows], table, experts, counts)
     else:
-        choice, weight = moe_route(h, router, correction, experts, top, counts)
+        choice, weight = moe_route(h, router, correction, experts, top, counts, scoring)
     ints = torch.empty(2 * pairs + experts + 1 + 3 * max_tiles + 1, dtype=torch.int32, device=device)
     place, source = ints[:pairs], ints[pairs: 2 * pairs]
     offsets = ints[2 * pairs: 2 * pairs + experts + 1]
@@ -1512,11 +1656,20 @@ def moe_experts(h: torch.Tensor, router: torch.Tensor | None, correction: torch.
               _ptr(source), rows, top, experts, max_tiles, tile_rows, _stream()), "moe_plan")
     act = torch.empty(pairs, inner, dtype=h.dtype, device=device)
     out = torch.empty(pairs, hidden, dtype=h.dtype, device=device)
-    if tcgen05:
+    sorted_rows = None
+    if weigh == "input":
+        # The weighted rows in sorted order; rows past the last sorted one (identity choices) stay unread.
         sorted_rows = torch.empty(pairs, hidden, dtype=h.dtype, device=device)
-        fn = _function("moe", "omnia_moe_gather", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-        _check(fn(_ptr(h), _ptr(source), _ptr(offsets[experts:]), _ptr(sorted_rows), pairs, hidden, _code(h.dtype),
-                  _stream()), "moe_gather")
+        fn = _function("moe", "omnia_moe_weighted_rows",
+                       [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_ptr(h), _ptr(place), _ptr(weight), _ptr(sorted_rows), pairs, hidden, top, _code(h.dtype), _stream()),
+               "moe_weighted_rows")
+    if tcgen05:
+        if sorted_rows is None:
+            sorted_rows = torch.empty(pairs, hidden, dtype=h.dtype, device=device)
+            fn = _function("moe", "omnia_moe_gather", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+            _check(fn(_ptr(h), _ptr(source), _ptr(offsets[experts:]), _ptr(sorted_rows), pairs, hidden, _code(h.dtype),
+                      _stream()), "moe_gather")
         grouped = _function("gemm_tcgen05", "omnia_gemm_tcgen05_grouped",
                             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                              c_float, c_float, c_void_p, c_void_p])
@@ -1529,15 +1682,16 @@ def moe_experts(h: torch.Tensor, router: torch.Tensor | None, correction: torch.
         product = _function("moe", "omnia_moe_product",
                             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_float, c_float, c_int, c_int, c_void_p])
-        _check(product(_ptr(h), _ptr(source), _ptr(gate_up), _ptr(act), _ptr(tiles), _ptr(tile_count), max_tiles, inner,
+        _check(product(_ptr(h if sorted_rows is None else sorted_rows), _ptr(source) if sorted_rows is None else None,
+                       _ptr(gate_up), _ptr(act), _ptr(tiles), _ptr(tile_count), max_tiles, inner,
                        hidden, 1, alpha, limit, _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
         _check(product(_ptr(act), None, _ptr(down), _ptr(out), _ptr(tiles), _ptr(tile_count), max_tiles, hidden, inner, 0,
                        1.0, 0.0, _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
     y = torch.empty_like(h)
     fn = _function("moe", "omnia_moe_combine",
-                   [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_ptr(out), _ptr(h), _ptr(place), _ptr(weight), _ptr(y), rows, hidden, top, _code(h.dtype), _stream()),
-           "moe_combine")
+                   [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(out), _ptr(h), _ptr(place), _ptr(weight) if weigh == "output" else None, _ptr(extra), _ptr(y), rows,
+              hidden, top, _code(h.dtype), _stream()), "moe_combine")
     return y
 
 

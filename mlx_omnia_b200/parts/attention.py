@@ -207,11 +207,15 @@ class SinkWindowAttention(Mixer):
     keep_first: with a window, how many of the request's first positions stay visible behind it
                 (they keep their own positions for the rotation)
     norm_eps:   None, or the eps of an RMS norm of every q and k head, with a weight of the head's size
-                shared by the heads (tensors `q.norm`, `k.norm`), applied before the rotation
+                shared by the heads (tensors `q.norm`, `k.norm`), applied before the rotation;
+    norm_weight: False for that norm without weights (no such tensors)
     position:   PartSpec of a half-split rotary encoding over the first `dims` <= dim of a head
     bias:       q, k and v projections have biases (`q.b`, `k.b`, `v.b`), added before the norm
-    sink:       the softmax's denominator also holds exp(sink_h), one learned number a head (`sink`),
-                unscaled, with no key and no value
+    sink:       True: the softmax's denominator also holds exp(sink_h), one learned number a head
+                (`sink`), unscaled, with no key and no value; "zero": the same with every sink_h = 0 and no
+                tensor, i.e. a one added to the denominator
+    values:     "own": a value projection `v`; "keys": there is none, and the values are the projected
+                keys as the product leaves them, ahead of the norm and the rotation (no biases; vdim = dim)
     own_kv:     False for a layer without k/v tensors that reads another layer's cache (as that cache
                 holds the keys: normed and rotated) with queries, window and sink of its own
     norm_over:  "head": the norm above, every head by itself; "projection": one root mean square over
@@ -234,7 +238,7 @@ class SinkWindowAttention(Mixer):
                  window: int | None = None, keep_first: int = 0, norm_eps: float | None = None,
                  position: PartSpec | None = None, bias: bool = False, sink: bool = False, own_kv: bool = True,
                  norm_over: str = "head", gated: bool = False, chunk: int | None = None,
-                 softcap: float | None = None) -> None:
+                 softcap: float | None = None, norm_weight: bool = True, values: str = "own") -> None:
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads do not divide into {kv_heads} groups")
         if dim > 256 or vdim > 256:
@@ -247,6 +251,11 @@ class SinkWindowAttention(Mixer):
             raise ValueError("chunk is a positive number of positions, and keeps no first positions")
         if softcap is not None and softcap <= 0:
             raise ValueError(f"softcap must be positive, got {softcap}")
+        if sink not in (False, True, "zero"):
+            raise ValueError(f"sink is False, True or 'zero', not {sink!r}")
+        if values not in ("own", "keys") or (values == "keys" and (vdim != dim or bias)):
+            raise ValueError("values are 'own' or, without biases and with vdim = dim, 'keys'")
+        self.norm_weight, self.values = bool(norm_weight), values
         self.hidden, self.heads, self.kv_heads, self.dim, self.vdim = hidden, heads, kv_heads, dim, vdim
         self.scale, self.window, self.keep_first, self.norm_eps = float(scale), window, int(keep_first), norm_eps
         self.bias, self.sink, self.own_kv = bias, sink, own_kv
@@ -266,30 +275,33 @@ class SinkWindowAttention(Mixer):
         if self.bias:
             specs["q.b"] = TensorSpec((H * dk,))
         whole = self.norm_over == "projection"
-        if self.norm_eps is not None:
+        if self.norm_eps is not None and self.norm_weight:
             specs["q.norm"] = TensorSpec((H * dk if whole else dk,), "vector")
-        if self.sink:
+        if self.sink is True:
             specs["sink"] = TensorSpec((H,), "vector")
         if self.gated:
             specs["g"] = TensorSpec((H * dv, self.hidden))
         if self.own_kv:
-            specs["k"], specs["v"] = TensorSpec((G * dk, self.hidden)), TensorSpec((G * dv, self.hidden))
+            specs["k"] = TensorSpec((G * dk, self.hidden))
+            if self.values == "own":
+                specs["v"] = TensorSpec((G * dv, self.hidden))
             if self.bias:
                 specs["k.b"], specs["v.b"] = TensorSpec((G * dk,)), TensorSpec((G * dv,))
-            if self.norm_eps is not None:
+            if self.norm_eps is not None and self.norm_weight:
                 specs["k.norm"] = TensorSpec((G * dk if whole else dk,), "vector")
         return specs
 
     def load(self, tensors, runtime) -> None:
         super().load(tensors, runtime)
         self.position.load({}, runtime)
-        names = ["q", "k", "v"] if self.own_kv else ["q"]
+        names = (["q", "k", "v"] if self.values == "own" else ["q", "k"]) if self.own_kv else ["q"]
         if self.gated:
             names.append("g")  # last, so that the columns of q, k and v stay where they are without it
         rows = [tensors[name] for name in names]
         self.k_col = self.heads * self.dim
-        self.v_col = self.k_col + self.kv_heads * self.dim
-        self.gate_col = (self.v_col + self.kv_heads * self.vdim) if self.own_kv else self.k_col
+        # Values that are the keys are read from the keys' columns of the projected rows.
+        self.v_col = self.k_col + (self.kv_heads * self.dim if self.values == "own" else 0)
+        self.gate_col = self.k_col + sum(r.shape[0] for r in rows[1:len(names) - int(self.gated)])
         total = sum(r.shape[0] for r in rows)
         pad = -total % 8  # rows of the operand in steps of 8, for the kernels that want them so
         if pad:
@@ -302,9 +314,14 @@ class SinkWindowAttention(Mixer):
             if pad:
                 parts.append(torch.zeros(pad, dtype=parts[0].dtype, device=parts[0].device))
             self.in_bias = torch.cat(parts).contiguous()
-        self.q_norm = tensors["q.norm"].contiguous() if self.norm_eps is not None else None
-        self.k_norm = tensors["k.norm"].contiguous() if self.norm_eps is not None and self.own_kv else None
-        self.sink_logits = tensors["sink"].contiguous() if self.sink else None
+        weighted = self.norm_eps is not None and self.norm_weight
+        self.q_norm = tensors["q.norm"].contiguous() if weighted else None
+        self.k_norm = tensors["k.norm"].contiguous() if weighted and self.own_kv else None
+        self.sink_logits = None
+        if self.sink is True:
+            self.sink_logits = tensors["sink"].contiguous()
+        elif self.sink == "zero":
+            self.sink_logits = torch.zeros(self.heads, dtype=torch.float32, device=runtime.device)
         self.o = tensors["o"].contiguous()
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:

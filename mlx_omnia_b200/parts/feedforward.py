@@ -167,16 +167,24 @@ class RoutedExperts(FeedForward):
     The router's logits are taken in float32 (its matrix is kept in float32 whatever the engine's
     dtype), the scores are a softmax over all experts + identity outputs; the choice is by score +
     `correction`, the weight is the score itself, not renormalised.
+    scoring:  "softmax" (above) or "sigmoid": every output's score is its own sigmoid
+    weigh:    "output": y = sum of score * expert(h); "input": y = sum of expert(score * h), the chosen
+              expert is given the token multiplied by its score and its output counts as it is
+    shared_inner: None, or the inner width of one more gated expert (`shared.gate`, `shared.up`,
+              `shared.down`) that every token uses unweighted and whose output is added
     Tensors: `router` [experts + identity, hidden], `correction` [experts + identity], and per expert i
     `e<i>.gate`, `e<i>.up` [inner, hidden], `e<i>.down` [hidden, inner] (stacked at load).
     """
 
     def __init__(self, hidden: int, inner: int, experts: int, top: int, identity: int = 0,
-                 correction: bool = True) -> None:
+                 correction: bool = True, scoring: str = "softmax", weigh: str = "output",
+                 shared_inner: int | None = None) -> None:
         if experts < 1 or identity < 0 or not 1 <= top <= experts + identity:
             raise ValueError(f"routed_experts of {experts} experts and {identity} identity ones, {top} a token")
+        if scoring not in ("softmax", "sigmoid") or weigh not in ("output", "input"):
+            raise ValueError(f"routed_experts scoring {scoring!r}, weigh {weigh!r}")
         self.hidden, self.inner, self.experts, self.identity, self.top = hidden, inner, experts, identity, top
-        self.corrected = correction
+        self.corrected, self.scoring, self.weigh, self.shared_inner = correction, scoring, weigh, shared_inner
 
     def tensors(self) -> dict[str, TensorSpec]:
         outputs = self.experts + self.identity
@@ -187,6 +195,10 @@ class RoutedExperts(FeedForward):
             specs[f"e{e}.gate"] = TensorSpec((self.inner, self.hidden))
             specs[f"e{e}.up"] = TensorSpec((self.inner, self.hidden))
             specs[f"e{e}.down"] = TensorSpec((self.hidden, self.inner))
+        if self.shared_inner is not None:
+            specs["shared.gate"] = TensorSpec((self.shared_inner, self.hidden))
+            specs["shared.up"] = TensorSpec((self.shared_inner, self.hidden))
+            specs["shared.down"] = TensorSpec((self.hidden, self.shared_inner))
         return specs
 
     def load(self, tensors, runtime) -> None:
@@ -196,6 +208,14 @@ class RoutedExperts(FeedForward):
         self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
                                     for e in range(self.experts)]).contiguous()
         self.down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
+        self.shared_gate_up = self.shared_down = None
+        if self.shared_inner is not None:
+            self.shared_gate_up = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0).contiguous()
+            self.shared_down = tensors["shared.down"].contiguous()
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
-        return ops.moe_experts(h, self.router, self.correction, self.gate_up, self.down, self.top, ctx.step)
+        extra = None
+        if self.shared_gate_up is not None:
+            extra = ops.linear(ops.linear_swiglu(h, self.shared_gate_up), self.shared_down)
+        return ops.moe_experts(h, self.router, self.correction, self.gate_up, self.down, self.top, ctx.step,
+                               scoring=self.scoring, weigh=self.weigh, extra=extra)

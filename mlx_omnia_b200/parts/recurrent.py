@@ -10,6 +10,17 @@ and projected out.
 `decay_attention` is linear attention with one constant decay per head: per head S <- decay_h S +
 k v^T and o = S^T q with q, k and v behind SiLU and no other scale; the heads' outputs side by side
 are RMS-normed together, weighted, gated by sigmoid(g(h)), and projected out.
+
+`gated_state_attention` is linear attention whose decay is a constant per head or a factor per token
+and key channel that the token sets through a low-rank map: S <- diag(a) S + k v^T, o = S^T q, with q
+and k optionally rotated and scaled in float32, every head's o divided by its own root mean square,
+and a silu or sigmoid gate.
+
+`gated_channel_recurrence` is a recurrent block with one number of state a channel: a short causal
+convolution, gates that are sigmoids of block-diagonal maps, S <- a S + sqrt(1 - a^2) i u with
+a = exp(-c r softplus(lam)), the output multiplied by a tanh-GELU branch.
+
+`side_by_side` runs two mixers on the same input and adds their outputs with a constant each.
 """
 
 from __future__ import annotations
@@ -17,7 +28,7 @@ from __future__ import annotations
 import torch
 
 from mlx_omnia_b200.kernels import ops
-from mlx_omnia_b200.parts.base import Mixer, StateSpec, TensorSpec, register_mixer
+from mlx_omnia_b200.parts.base import MIXERS, POSITIONS, LayerContext, Mixer, PartSpec, StateSpec, TensorSpec, register_mixer
 
 
 @register_mixer("channel_delta")
@@ -150,3 +161,213 @@ class DecayAttention(Mixer):
         out = ops.lightning_attention(proj, 0, self.k_col, self.v_col, self.gate_col, self.heads, self.dim, self.vdim,
                                       self.decays, self.norm_weight, self.norm_eps, ctx.state, ctx.step)
         return ops.linear(out, self.o)
+
+
+@register_mixer("gated_state_attention")
+class GatedStateAttention(Mixer):
+    """hidden: model width; heads of `dim` (queries and keys) and `vdim` (values); norm_eps: eps under
+    the root of the heads' output norms.
+    decay:      a constant in (0, 1] per head, or None for a decay per token and key channel,
+                a = sigmoid(a2 (a1 h) + a2.b)^(1 / tau), with `decay_rank` the inner width of the map
+    position:   None, or the PartSpec of a half-split rotary encoding applied to q and k (float32)
+    q_scale, k_scale: multiply q and k after the rotation (float32)
+    norm_weight: the heads' output norm has a weight `norm` [vdim] that the heads share
+    gate:       "silu" or "sigmoid" of g h, multiplied into the normed outputs
+
+    Tensors: q, k [heads * dim, hidden]; v, g [heads * vdim, hidden]; o [hidden, heads * vdim];
+    norm [vdim]; a1 [decay_rank, hidden], a2 [heads * dim, decay_rank], a2.b [heads * dim].
+    State (float32): S [heads, dim, vdim], zeros at a request's start."""
+
+    graph_safe = True
+    graph_safe_mixed = True
+
+    def __init__(self, hidden: int, heads: int, dim: int, vdim: int, norm_eps: float,
+                 decay: tuple[float, ...] | None = None, decay_rank: int = 0, tau: float = 1.0,
+                 position: PartSpec | None = None, q_scale: float = 1.0, k_scale: float = 1.0,
+                 norm_weight: bool = True, gate: str = "silu") -> None:
+        if decay is not None:
+            decay = tuple(float(d) for d in decay)
+            if len(decay) != heads:
+                raise ValueError(f"gated_state_attention of {heads} heads was given {len(decay)} decays")
+        elif decay_rank < 1 or tau <= 0:
+            raise ValueError("a decay per channel needs the inner width of its map and a positive tau")
+        if dim < 1 or dim > 256 or vdim < 1:
+            raise ValueError(f"gated_state_attention takes keys of 1 to 256 and values of at least 1, got {dim} and {vdim}")
+        if gate not in ("silu", "sigmoid"):
+            raise ValueError(f"the gate is 'silu' or 'sigmoid', not {gate!r}")
+        self.hidden, self.heads, self.dim, self.vdim, self.norm_eps = hidden, heads, dim, vdim, float(norm_eps)
+        self.decay, self.decay_rank, self.tau = decay, int(decay_rank), float(tau)
+        self.q_scale, self.k_scale, self.norm_weight, self.gate = float(q_scale), float(k_scale), bool(norm_weight), gate
+        self.position = POSITIONS.build(position or PartSpec("none"))
+        if getattr(self.position, "pairing", "half") != "half":
+            raise ValueError("gated_state_attention rotates half-split pairs")
+        if getattr(self.position, "dims", 0) > dim:
+            raise ValueError(f"{self.position.dims} rotary dims do not fit a head of {dim}")
+
+    def state_spec(self):
+        return StateSpec((self.heads, self.dim, self.vdim), torch.float32)
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        qk, v, d = self.heads * self.dim, self.heads * self.vdim, self.hidden
+        specs = {"q": TensorSpec((qk, d)), "k": TensorSpec((qk, d)), "v": TensorSpec((v, d)), "g": TensorSpec((v, d)),
+                 "o": TensorSpec((d, v))}
+        if self.norm_weight:
+            specs["norm"] = TensorSpec((self.vdim,), "vector")
+        if self.decay is None:
+            specs.update({"a1": TensorSpec((self.decay_rank, d)), "a2": TensorSpec((qk, self.decay_rank)),
+                          "a2.b": TensorSpec((qk,), "vector")})
+        return specs
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        self.position.load({}, runtime)
+        # One operand [q | k | v | g | a1] (rows padded to a multiple of 8): a single input projection.
+        names = ["q", "k", "v", "g"] + (["a1"] if self.decay is None else [])
+        rows = [tensors[name] for name in names]
+        qk, v = self.heads * self.dim, self.heads * self.vdim
+        self.k_col, self.v_col, self.gate_col, self.a1_col = qk, 2 * qk, 2 * qk + v, 2 * qk + 2 * v
+        total = sum(r.shape[0] for r in rows)
+        if total % 8:
+            rows.append(torch.zeros(8 - total % 8, self.hidden, dtype=rows[0].dtype, device=rows[0].device))
+        self.in_proj = torch.cat(rows, dim=0).contiguous()
+        self.norm = tensors["norm"].contiguous() if self.norm_weight else None
+        self.o = tensors["o"].contiguous()
+        self.decays = self.a2 = self.a2_bias = None
+        if self.decay is not None:
+            self.decays = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(runtime.device)
+        else:
+            self.a2, self.a2_bias = tensors["a2"].contiguous(), tensors["a2.b"].contiguous()
+
+    def forward(self, h, ctx) -> torch.Tensor:
+        proj = ops.linear(h, self.in_proj)
+        logits = None
+        if self.decay is None:
+            logits = ops.linear(proj[:, self.a1_col: self.a1_col + self.decay_rank], self.a2)
+        out = ops.state_attention(proj, 0, self.k_col, self.v_col, self.gate_col, self.heads, self.dim, self.vdim,
+                                  ctx.state, ctx.step, self.norm_eps, decay=self.decays, decay_logits=logits,
+                                  decay_bias=self.a2_bias, tau=self.tau, inv_freq=self.position.table(),
+                                  q_scale=self.q_scale, k_scale=self.k_scale, norm_weight=self.norm, gate=self.gate)
+        return ops.linear(out, self.o)
+
+
+@register_mixer("gated_channel_recurrence")
+class GatedChannelRecurrence(Mixer):
+    """hidden: model width; width: channels of the recurrence, cut into `blocks` equal runs for the
+    gates' block-diagonal maps; conv: taps of the causal convolution; c_decay: the constant c in
+    a = exp(-c r softplus(lam)).
+
+    Two branches read the input: y = gelu_tanh(y h + y.b) and u = conv(x h + x.b) (taps `conv`
+    [width, taps], the last column the current token's, bias `conv.b`; zeros ahead of a request's
+    start). Per run b of u: r = sigmoid(ra[b] u_b + ra.b[b]), i = sigmoid(ri[b] u_b + ri.b[b]) with
+    ra[b], ri[b] square [out, in]. S <- a S + sqrt(1 - a^2) i u from S = 0; out = o (S * y).
+
+    Tensors: x, y [width, hidden], x.b, y.b [width]; conv [width, taps], conv.b [width]; ra, ri
+    [blocks, width / blocks, width / blocks], ra.b, ri.b [blocks, width / blocks]; lam [width];
+    o [hidden, width].
+    State (float32): S [width] and the convolution's last taps - 1 inputs."""
+
+    graph_safe = True
+    graph_safe_mixed = True
+
+    def __init__(self, hidden: int, width: int, blocks: int, conv: int, c_decay: float = 8.0) -> None:
+        if blocks < 1 or width % blocks:
+            raise ValueError(f"{width} channels do not divide into {blocks} blocks")
+        if not 1 <= conv <= ops.RGLRU_MAX_TAPS:
+            raise ValueError(f"a convolution of {conv} taps (1 to {ops.RGLRU_MAX_TAPS})")
+        self.hidden, self.width, self.blocks, self.conv, self.c_decay = hidden, width, blocks, conv, float(c_decay)
+
+    def state_spec(self):
+        return {"S": StateSpec((self.width,), torch.float32),
+                "conv": StateSpec((max(self.conv - 1, 1), self.width), torch.float32)}
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        w, d, b, bw = self.width, self.hidden, self.blocks, self.width // self.blocks
+        return {"x": TensorSpec((w, d)), "y": TensorSpec((w, d)), "x.b": TensorSpec((w,), "vector"),
+                "y.b": TensorSpec((w,), "vector"), "conv": TensorSpec((w, self.conv), "vector"),
+                "conv.b": TensorSpec((w,), "vector"), "ra": TensorSpec((b, bw, bw), "vector"),
+                "ri": TensorSpec((b, bw, bw), "vector"), "ra.b": TensorSpec((b, bw), "vector"),
+                "ri.b": TensorSpec((b, bw), "vector"), "lam": TensorSpec((w,), "vector"), "o": TensorSpec((d, w))}
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        rows = [tensors["x"], tensors["y"]]  # one operand [x | y]
+        if 2 * self.width % 8:
+            rows.append(torch.zeros(8 - 2 * self.width % 8, self.hidden, dtype=rows[0].dtype, device=rows[0].device))
+        self.in_proj = torch.cat(rows, dim=0).contiguous()
+        self.x_bias, self.y_bias = tensors["x.b"].contiguous(), tensors["y.b"].contiguous()
+        self.taps, self.conv_bias = tensors["conv"].contiguous(), tensors["conv.b"].contiguous()
+        # Both gates' maps side by side, input channels along the rows: [blocks, in, r's out | i's out], float32.
+        self.gates = torch.cat([tensors["ra"].transpose(1, 2), tensors["ri"].transpose(1, 2)], dim=2).contiguous()
+        self.r_bias, self.i_bias = tensors["ra.b"].reshape(-1).contiguous(), tensors["ri.b"].reshape(-1).contiguous()
+        self.lam, self.o = tensors["lam"].contiguous(), tensors["o"].contiguous()
+
+    def forward(self, h, ctx) -> torch.Tensor:
+        proj = ops.linear(h, self.in_proj)
+        out = ops.gated_channel_recurrence(proj, 0, self.width, self.x_bias, self.y_bias, self.taps, self.conv_bias,
+                                           self.gates, self.r_bias, self.i_bias, self.lam, self.c_decay, ctx.state["S"],
+                                           ctx.state["conv"], ctx.step)
+        return ops.linear(out, self.o)
+
+
+@register_mixer("side_by_side")
+class SideBySide(Mixer):
+    """Two mixers that read the same input; the result is left_scale * left(h) + right_scale * right(h),
+    the sum taken in float32 and rounded once.
+
+    left, right: PartSpecs of registered mixers; their tensors sit under `left.` and `right.`. At most
+    one of the two may keep rows in the paged cache (the schedule entry's pages are that one's); each
+    may keep per-request state, which this part hands to its owner."""
+
+    def __init__(self, left: PartSpec, right: PartSpec, left_scale: float = 1.0, right_scale: float = 1.0) -> None:
+        self.sides = {"left": MIXERS.build(left), "right": MIXERS.build(right)}
+        self.scales = {"left": float(left_scale), "right": float(right_scale)}
+        if sum(side.kv_spec() is not None for side in self.sides.values()) > 1:
+            raise ValueError("side_by_side takes at most one mixer that keeps rows in the paged cache")
+        self.graph_safe = all(getattr(side, "graph_safe", False) for side in self.sides.values())
+        self.graph_safe_mixed = all(getattr(side, "graph_safe_mixed", False) for side in self.sides.values())
+        self._stateful = [name for name, side in self.sides.items() if side.state_spec() is not None]
+
+    def kv_spec(self):
+        return next((spec for spec in (side.kv_spec() for side in self.sides.values()) if spec is not None), None)
+
+    def state_spec(self):
+        if not self._stateful:
+            return None
+        if len(self._stateful) == 1:
+            return self.sides[self._stateful[0]].state_spec()
+        merged = {}
+        for name in self._stateful:
+            spec = self.sides[name].state_spec()
+            for key, value in (spec.items() if isinstance(spec, dict) else [("", spec)]):
+                merged[f"{name}.{key}" if key else name] = value
+        return merged
+
+    def initial_state(self):
+        return self.sides[self._stateful[0]].initial_state() if len(self._stateful) == 1 else None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {f"{name}.{local}": spec for name, side in self.sides.items() for local, spec in side.tensors().items()}
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        for name, side in self.sides.items():
+            prefix = name + "."
+            side.load({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, runtime)
+
+    def _state_of(self, name: str, state):
+        if name not in self._stateful:
+            return None
+        if len(self._stateful) == 1:
+            return state
+        if isinstance(self.sides[name].state_spec(), dict):
+            prefix = name + "."
+            return {k[len(prefix):]: v for k, v in state.items() if k.startswith(prefix)}
+        return state[name]
+
+    def forward(self, h, ctx) -> torch.Tensor:
+        outs = {}
+        for name, side in self.sides.items():
+            mine = LayerContext(ctx.step, ctx.kv if side.kv_spec() is not None else None, self._state_of(name, ctx.state),
+                                ctx.entry, ctx.block_state, False)
+            outs[name] = side.forward(h, mine)
+        return ops.scaled_sum(outs["left"], self.scales["left"], outs["right"], self.scales["right"])
