@@ -132,7 +132,7 @@ def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor) -> torc
     """x [T, C], taps [C, K]: y_t = bias + sum_j taps[:, K - 1 - j] x_(t - j), zeros ahead of the start."""
     T, K = x.shape[0], taps.shape[1]
     y = bias.to(x.dtype).expand(T, -1).clone()
-    for j in range(K):
+    for j in range(min(K, T)):
         y[j:] += x[: T - j] * taps[:, K - 1 - j].to(x.dtype)
     return y
 
