@@ -27,7 +27,10 @@ routed experts), beside Muse-Glimmer with sliding attention at equal width, dept
 active feed-forward width. `--only bobarax` is that record for the Bobarax design (decayed linear attention,
 run-masked attention with capped scores, gated windowed attention, experts chosen by a table), beside Dolutar
 at equal width, depth, heads, window and experts; its kernels stand beside the like kernels of Dolutar and,
-for the recurrence, of Fokalorn.
+for the recurrence, of Fokalorn. `--only narezen` is that record for the Narezen design (attention beside a
+decayed linear-attention state in one mixer, a gated recurrence over channels, sigmoid-routed experts weighted
+on their inputs with a shared expert), beside Bobarax at equal width, depth, heads and experts; its kernels
+stand beside the like kernels of Bobarax.
 """
 
 from __future__ import annotations
@@ -1278,6 +1281,249 @@ def run_bobarax(args) -> dict:
                                  "kernels": kernels(size), "layers": size["layers"]}
     return record
 
+def narezen_config(size: dict) -> dict:
+    """Layers in fours: attention whose values are its keys beside a channel-decayed state, rotated attention
+    beside a retention, a gated recurrence over channels, and the first kind again; experts with a shared
+    expert everywhere. The linear-attention sides have half the attention's heads, of the same widths."""
+    H, G, d, D = size["heads"], size["kv"], size["dim"], size["width"]
+    R = max(H // 2, 1)
+    moe = {"kind": "moe", "expert": {"ff": size["eff"]}, "router": {"experts": size["experts"], "top": size["top"]},
+           "shared": {"ff": size["eff"]}}
+    layers = []
+    for i in range(size["layers"]):
+        kind = i % 4
+        if kind in (0, 3):
+            mixer = {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": 0.125},
+                     "right": {"heads": R, "dim": d, "vdim": d, "tau": 16.0}, "left_scale": 1.2, "right_scale": 1.1}
+            layers.append({"type": "parallel", "mixer": mixer, "mlp": moe})
+        elif kind == 1:
+            decay = [1.0 - 2.0 ** -(5 + 6 * h / max(R - 1, 1)) for h in range(R)]
+            mixer = {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5,
+                              "rot": {"base": 100000.0, "dims": d // 2}},
+                     "right": {"heads": R, "dim": d, "vdim": d, "decay": decay, "rot": {"base": 1e6, "dims": d}},
+                     "left_scale": 1.2, "right_scale": 0.5}
+            layers.append({"type": "parallel_2", "mixer": mixer, "mlp": moe})
+        else:
+            layers.append({"type": "rglru", "mixer": {"width": D, "blocks": H, "conv": 4}, "mlp": moe})
+    return {"architecture": "Narezen", "vocab": DOLUTAR_VOCAB, "width": D, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "logit_softcap": 30.0, "layers": layers}
+
+
+def run_narezen(args) -> dict:
+    """Prefill (one prompt of --prefill-tokens) and decode (--batch requests ending at --context tokens)
+    of Narezen and of Bobarax at equal sizes, then the new design's kernels alone, each beside the like
+    kernel of Bobarax."""
+    import torch
+
+    from mlx_omnia_b200.engine.engine import Engine, EngineArgs
+    from mlx_omnia_b200.engine.step import StepEntry
+    from mlx_omnia_b200.kernels import ops
+    from mlx_omnia_b200.parts.base import KVSpec, KVView
+
+    measured, peak_source = peaks()
+    hbm, flops_peak = measured["hbm_gbs"] * 1e9, measured["bf16_tflops"] * 1e12
+    g = torch.Generator().manual_seed(SEED)
+    steps, warmup, batch, context, tokens = args.steps, max(args.warmup, 3), args.batch, args.context, args.prefill_tokens
+    dev, bf = torch.device("cuda:0"), torch.bfloat16
+    vocab = DOLUTAR_VOCAB
+
+    def timed(fn, count, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(count):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / count
+
+    def whole_model(raw) -> dict:
+        engine = Engine.from_random(raw, SEED, EngineArgs(dtype="bfloat16", page_size=16, max_requests=batch + 1,
+                                                          cache_tokens=batch * (context + 16) + tokens + 16))
+        times = []
+        for index in range(warmup + 3):
+            request = engine.cache.open(f"p{index}")
+            ids = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.runner.run([StepEntry(request, ids, [tokens - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            engine.cache.close(request.request_id)
+            times.append(start.elapsed_time(stop))
+        prefill_ms = statistics.median(times[warmup:])
+        requests = [engine.cache.open(f"d{i}") for i in range(batch)]
+        length = context - steps - warmup - 1
+        for r in requests:
+            engine.runner.run([StepEntry(r, torch.randint(0, vocab, (length,), generator=g).tolist(), [])])
+        entries = lambda i: [StepEntry(r, [1 + i], [0]) for r in requests]
+        for i in range(warmup):
+            engine.runner.run(entries(i), copy=False)
+        torch.cuda.synchronize()
+        launches = ops.launches
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            engine.runner.run(entries(warmup + i), copy=False)
+        stop.record()
+        torch.cuda.synchronize()
+        decode_ms = start.elapsed_time(stop) / steps
+        ops.raise_on_error(engine.runtime.device)
+        out = {"prefill_tokens_per_s": round(tokens * 1000.0 / prefill_ms, 1), "prefill_ms": round(prefill_ms, 3),
+               "decode_tokens_per_s": round(batch * 1000.0 / decode_ms, 1), "decode_ms": round(decode_ms, 4),
+               "launches_per_decode_step": (ops.launches - launches) // steps}
+        for r in requests:
+            engine.cache.close(r.request_id)
+        del engine
+        torch.cuda.empty_cache()
+        return out
+
+    class Step:
+        pass
+
+    def step_of(lens, starts):
+        st = Step()
+        st.num_seqs, st.q_lens = len(lens), list(lens)
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        st.num_tokens = cu[-1]
+        st.cu_seqlens = torch.tensor(cu, dtype=torch.int32, device=dev)
+        st.state_slots = torch.arange(len(lens), dtype=torch.int32, device=dev)
+        st.positions = torch.tensor([s + i for s, n in zip(starts, lens) for i in range(n)], dtype=torch.int32, device=dev)
+        st.seq_lens = torch.tensor([s + n for s, n in zip(starts, lens)], dtype=torch.int32, device=dev)
+        st.seq_lens_host, st.max_q_len = [s + n for s, n in zip(starts, lens)], max(lens)
+        st.max_seq_len = max(st.seq_lens_host)
+        st.decode_only, st.workspace = all(n == 1 for n in lens), None
+        return st
+
+    def kernels(size: dict) -> dict:
+        H, G, d, D = size["heads"], size["kv"], size["dim"], size["width"]
+        R = max(H // 2, 1)
+        E, top, F = size["experts"], size["top"], size["eff"]
+        out = {}
+
+        def note(name, ms, bytes_=None, flops=None):
+            entry = {"us": round(ms * 1000.0, 2)}
+            if bytes_ is not None:
+                entry.update(gb_s=round(bytes_ / ms / 1e6, 1), frac_hbm=round(bytes_ / (ms / 1e3) / hbm, 4))
+            if flops is not None:
+                entry.update(tflops=round(flops / ms / 1e9, 2), frac_tensor=round(flops / (ms / 1e3) / flops_peak, 4))
+            out[name] = entry
+
+        for mode, lens, starts in (("prefill", [tokens], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+            st = step_of(lens, starts)
+            T = sum(lens)
+            page = 16
+            pages = -(-st.max_seq_len // page)
+            table = torch.arange(len(lens) * pages, dtype=torch.int32, device=dev).view(len(lens), pages)
+            slots = torch.cat([table[i].long()[(st.positions[st.cu_seqlens[i]: st.cu_seqlens[i + 1]] // page).long()] * page
+                               + st.positions[st.cu_seqlens[i]: st.cu_seqlens[i + 1]].long() % page for i in range(len(lens))])
+            cache = (torch.randn(len(lens) * pages, 2, G, page, d, device=dev) * 0.3).to(bf)
+            kv = KVView(cache, table, slots, page, None, True, KVSpec(((G, d), (G, d))))
+            # the input step of the attention whose values are its keys (weightless head norms, no rotation), beside
+            # Bobarax's (one norm over the projection, rotation of neighbouring pairs)
+            cols = (H + G) * d
+            proj = (torch.randn(T, cols + G * d + H * d, device=dev) * 0.5).to(bf)
+            ms = timed(lambda: ops.qkv_prepare(proj, 0, H * d, H * d, H, d, None, None, None, 1e-5, None, st.positions, kv, True), 20)
+            note(f"qkv_prepare_keys_as_values_{mode}", ms, bytes_=T * (cols * 2 + (H + 2 * G) * d * 2))
+            inv = torch.tensor([100000.0 ** (-2.0 * i / (d // 2)) for i in range(d // 4)], device=dev)
+            wq, wk = torch.ones(H * d, device=dev), torch.ones(G * d, device=dev)
+            ms = timed(lambda: ops.qkv_prepare(proj, 0, H * d, (H + G) * d, H, d, None, wq, wk, 1e-5, inv, st.positions, kv, True,
+                                               whole=True, interleaved=True), 20)
+            note(f"like:qkv_prepare_whole_{mode}", ms, bytes_=T * (H + 2 * G) * d * 4)
+            # causal attention over every earlier position with a sink a head, beside Bobarax's windowed attention
+            # with its gate (a window as long as the context sees the same keys)
+            q = (torch.randn(T, H, d, device=dev) * 0.3).to(bf)
+            sink = torch.zeros(H, device=dev)
+            reps = 5 if mode == "prefill" else 20
+            seen = sum(s + i + 1 for s, n in zip(starts, lens) for i in range(n))
+            held = sum(s + n for s, n in zip(starts, lens))
+            work = dict(bytes_=held * 2 * G * d * 2 + 4 * T * H * d, flops=4 * seen * H * d)
+            ms = timed(lambda: ops.paged_attention(q, kv, st, 0.125, sink=sink), reps, 2)
+            note(f"sink_attention_{mode}", ms, **work)
+            wide = st.max_seq_len + 1
+            wkv = KVView(cache, table, slots, page, wide, True, KVSpec(((G, d), (G, d)), wide))
+            ms = timed(lambda: ops.paged_attention(q, wkv, st, d ** -0.5, gate=proj, gate_col=cols + G * d, window=wide), reps, 2)
+            note(f"like:window_gate_attention_{mode}", ms, **work)
+            # linear attention from a float32 state: a decay per key channel (with the input step that makes the
+            # decays), a decay per head with rotated queries and keys, beside Bobarax's recurrence of equal heads
+            lcols = 2 * R * d + 2 * R * d  # q | k | v | gate
+            lproj = (torch.randn(T, lcols, device=dev) * 0.5).to(bf)
+            z = (torch.randn(T, R * d, device=dev) + 2.0).to(bf)
+            zb = torch.zeros(R * d, device=dev)
+            S_state = torch.zeros(len(lens) + 1, R, d, d, device=dev)
+            decays = torch.full((R,), 0.99, device=dev)
+            nw, nwh = torch.ones(R * d, device=dev), torch.ones(d, device=dev)
+            rinv = torch.tensor([1e6 ** (-2.0 * i / d) for i in range(d // 2)], device=dev)
+            state_bytes = 2 * len(lens) * R * d * d * 4
+            moved = state_bytes + T * (4 * R * d * 2 + R * d * 2)
+            ms = timed(lambda: ops.state_attention(lproj, 0, R * d, 2 * R * d, 3 * R * d, R, d, d, S_state, st, 1e-5,
+                                                   decay_logits=z, decay_bias=zb, tau=16.0, q_scale=d ** -0.5, norm_weight=nwh), 10)
+            note(f"channel_decay_attention_{mode}", ms, bytes_=moved + T * R * d * 2, flops=T * R * d * d * 2 * 2)
+            S_state.zero_()
+            ms = timed(lambda: ops.state_attention(lproj, 0, R * d, 2 * R * d, 3 * R * d, R, d, d, S_state, st, 1e-5,
+                                                   decay=decays, inv_freq=rinv, k_scale=d ** -0.5), 10)
+            note(f"retention_{mode}", ms, bytes_=moved, flops=T * R * d * d * 2 * 2)
+            S_state.zero_()
+            ms = timed(lambda: ops.lightning_attention(lproj, 0, R * d, 2 * R * d, 3 * R * d, R, d, d, decays, nw, 1e-5, S_state, st), 10)
+            note(f"like:lightning_attention_{mode}", ms, bytes_=moved, flops=T * R * d * d * 2 * 2)
+            del S_state, lproj
+            # the gated recurrence over channels (convolution, block-diagonal gates, scan) of the model's width
+            C, blocks, K = D, H, 4
+            bw = C // blocks
+            rproj = (torch.randn(T, 2 * C, device=dev) * 0.5).to(bf)
+            xb, yb, cb, lam = (torch.zeros(C, device=dev) for _ in range(4))
+            taps = torch.randn(C, K, device=dev) * 0.5
+            gates = torch.randn(blocks, bw, 2 * bw, device=dev) * bw ** -0.5
+            rb, ib = torch.zeros(C, device=dev), torch.zeros(C, device=dev)
+            S1, conv_state = torch.zeros(len(lens) + 1, C, device=dev), torch.zeros(len(lens) + 1, K - 1, C, device=dev)
+            ms = timed(lambda: ops.gated_channel_recurrence(rproj, 0, C, xb, yb, taps, cb, gates, rb, ib, lam, 8.0, S1, conv_state, st), 10)
+            note(f"gated_channel_recurrence_{mode}", ms, bytes_=T * C * (2 * 2 + 2) + blocks * bw * 2 * bw * 4,
+                 flops=2 * T * C * 2 * bw)
+            del rproj
+            # the two sides' sum beside the residual step (the like pass over a row)
+            a, b = (torch.randn(T, D, device=dev).to(bf) for _ in range(2))
+            note(f"scaled_sum_{mode}", timed(lambda: ops.scaled_sum(a, 1.2, b, 1.1), 20), bytes_=T * D * 6)
+            x, w = torch.randn(T, D, device=dev), torch.ones(D, device=dev)
+            note(f"like:add_rmsnorm_{mode}", timed(lambda: ops.add_rmsnorm(x, a, w, 1e-5, w, 1e-5), 20), bytes_=T * D * (4 + 4 + 2 + 2))
+            # experts chosen by sigmoid scores and given the weighted token, with the shared expert, beside Bobarax's
+            # experts chosen by a table
+            h = (torch.randn(T, D, device=dev) * 0.5).to(bf)
+            egu = (torch.randn(E, 2 * F, D, device=dev) * D ** -0.5).to(bf)
+            edn = (torch.randn(E, D, F, device=dev) * F ** -0.5).to(bf)
+            sgu, sdn = (torch.randn(2 * F, D, device=dev) * D ** -0.5).to(bf), (torch.randn(D, F, device=dev) * F ** -0.5).to(bf)
+            rows = [torch.randperm(E, generator=g)[:top] for _ in range(4096)]
+            expert_table = torch.stack(rows).to(torch.int32).repeat(vocab // 4096, 1).to(dev).contiguous()
+            st.token_ids = torch.randint(0, vocab, (T,), device=dev, dtype=torch.int32)
+            router = torch.randn(E, D, device=dev) * 0.05
+            used = E * (1.0 - (1.0 - top / E) ** T)
+            work = dict(bytes_=used * 3 * F * D * 2 + T * D * 4, flops=2 * T * top * 3 * F * D)
+            ms = timed(lambda: ops.moe_experts(h, router, None, egu, edn, top, st, scoring="sigmoid", weigh="input"), 10)
+            note(f"sigmoid_input_weighted_experts_{mode}", ms, **work)
+            ms = timed(lambda: ops.moe_experts(h, None, None, egu, edn, top, st, table=expert_table, token_ids=st.token_ids,
+                                               alpha=1.702, limit=7.0), 10)
+            note(f"like:table_experts_{mode}", ms, **work)
+            ms = timed(lambda: ops.linear(ops.linear_swiglu(h, sgu), sdn), 10)
+            note(f"shared_expert_{mode}", ms, bytes_=3 * F * D * 2 + T * (2 * D + F) * 2, flops=2 * T * 3 * F * D)
+            del egu, edn
+        ops.raise_on_error(dev)
+        return out
+
+    record = {"metric": "Narezen beside Bobarax at equal sizes", "unit": "tokens/s", "dtype": "bf16",
+              "data": "synthetic: seeded uniform-random token ids, random weights",
+              "config": {"prefill_tokens": tokens, "decode_batch": batch, "decode_context": context, "vocab": vocab,
+                         "peaks": peak_source}, "sizes": {}}
+    for name in ([args.size] if args.size else list(BOBARAX_SIZES)):
+        size = BOBARAX_SIZES[name]
+        record["sizes"][name] = {"narezen": whole_model(narezen_config(size)), "bobarax": whole_model(bobarax_config(size)),
+                                 "kernels": kernels(size), "layers": size["layers"]}
+    return record
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -1290,7 +1536,7 @@ def main() -> int:
                         help="with --only decode|prefill and OMNIA_TIMELINE=1 in the environment: one step's "
                              "kernels with the time each takes in the stream, on stderr")
     parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "portions", "sampling", "products", "elementwise", "fokalorn",
-                                           "dolutar", "bobarax"], default="all",
+                                           "dolutar", "bobarax", "narezen"], default="all",
                         help="time one part only (small cases for profilers); prints a short record")
     parser.add_argument("--config", type=int, choices=sorted(CONFIGS), default=2,
                         help="with --only: the sizes of another benchmark configuration (3: 36 layers, hidden 4096, "
@@ -1302,7 +1548,7 @@ def main() -> int:
     parser.add_argument("--portion", type=int, default=256,
                         help="--only mixed: tokens of a prompt that run beside --batch decoding requests")
     parser.add_argument("--size", choices=sorted(FOKALORN_SIZES), default=None,
-                        help="--only fokalorn, dolutar or bobarax: one size instead of all")
+                        help="--only fokalorn, dolutar, bobarax or narezen: one size instead of all")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -1321,6 +1567,9 @@ def main() -> int:
         return 0
     if args.only == "bobarax":
         print(json.dumps(run_bobarax(args)))
+        return 0
+    if args.only == "narezen":
+        print(json.dumps(run_narezen(args)))
         return 0
     if args.only == "dolutar":
         print(json.dumps(run_dolutar(args)))

@@ -20,6 +20,11 @@
 //            writes S_t y_t. Then the block moves the convolution's state on (the last K - 1 inputs).
 //            The cut into segments depends on the portion's length only through rounding: a segment's
 //            start is S_before * (product of a) + (value from zero), the same recurrence regrouped.
+//
+//   step     a step in which every request brings one token (decoding) runs all of the above in one
+//            kernel: a block per (request, block of the gates' maps) makes its channels' u, takes the two
+//            maps' products with it from the float32 matrices (a thread an output, the additions in the
+//            order of the inputs), and moves S and the convolution's state on.
 #include "common.cuh"
 
 #define RGLRU_MAX_TAPS 16
@@ -153,6 +158,60 @@ __global__ void __launch_bounds__(32 * RGLRU_SCAN_WARPS) rglru_scan_kernel(
   }
 }
 
+// grid (blocks of the maps, requests); gates [blocks, bw (in), 2 bw (out: r's, then i's)].
+template <typename T>
+__global__ void __launch_bounds__(256) rglru_step_kernel(
+    const T* __restrict__ proj, int stride, int x_col, int y_col, const float* __restrict__ x_bias,
+    const float* __restrict__ y_bias, const float* __restrict__ taps, const float* __restrict__ conv_bias,
+    const float* __restrict__ gates, const float* __restrict__ r_bias, const float* __restrict__ i_bias,
+    const float* __restrict__ lam, float c_decay, int C, int bw, int K, float* __restrict__ S_state,
+    float* __restrict__ conv_state, const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
+    T* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
+  extern __shared__ float step_s[];  // u [bw] | z [2 bw]
+  float* u_s = step_s;
+  float* z_s = step_s + bw;
+  const int block = blockIdx.x, seq = blockIdx.y;
+  const int t = cu_seqlens[seq];
+  if (cu_seqlens[seq + 1] <= t) return;
+  const size_t slot = (size_t)state_slots[seq];
+  const int c0 = block * bw;
+  for (int o = threadIdx.x; o < bw; o += blockDim.x) {
+    const int c = c0 + o;
+    float* state = conv_state + slot * (K - 1) * C + c;  // [K - 1][C], oldest first
+    const float x = to_f32(proj[(size_t)t * stride + x_col + c]) + (x_bias ? x_bias[c] : 0.f);
+    float acc = conv_bias ? conv_bias[c] : 0.f;
+    acc = fmaf(taps[(size_t)c * K + K - 1], x, acc);
+    // The same order of additions as the kernel that walks a portion: the current token first, then back.
+    for (int j = 1; j < K; ++j) acc = fmaf(taps[(size_t)c * K + (K - 1 - j)], state[(size_t)(K - 1 - j) * C], acc);
+    for (int i = 0; i + 1 < K - 1; ++i) state[(size_t)i * C] = state[(size_t)(i + 1) * C];
+    if (K > 1) state[(size_t)(K - 2) * C] = x;
+    u_s[o] = acc;
+  }
+  __syncthreads();
+  const float* g = gates + (size_t)block * bw * 2 * bw;
+  for (int o = threadIdx.x; o < 2 * bw; o += blockDim.x) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < bw; ++i) acc = fmaf(g[(size_t)i * 2 * bw + o], u_s[i], acc);
+    z_s[o] = acc;
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < bw; o += blockDim.x) {
+    const int c = c0 + o;
+    const float r = 1.f / (1.f + expf(-(z_s[o] + r_bias[c])));
+    const float i = 1.f / (1.f + expf(-(z_s[bw + o] + i_bias[c])));
+    const float l = lam[c];
+    const float softplus = fmaxf(l, 0.f) + log1pf(expf(-fabsf(l)));
+    const float log_a = -c_decay * r * softplus;
+    const float S = fmaf(expf(log_a), S_state[slot * C + c], sqrtf(-expm1f(2.f * log_a)) * i * u_s[o]);
+    S_state[slot * C + c] = S;
+    const float y = gelu_tanh_f(to_f32(proj[(size_t)t * stride + y_col + c]) + (y_bias ? y_bias[c] : 0.f));
+    out[(size_t)t * C + c] = from_f32<T>(S * y);
+  }
+}
+
 }  // namespace
 
 extern "C" int omnia_rglru_max_taps(void) { return RGLRU_MAX_TAPS; }
@@ -194,6 +253,23 @@ extern "C" int omnia_rglru_scan(const float* a, const float* b, const float* y, 
   if (warps < 1 || warps > RGLRU_SCAN_WARPS || K < 1 || K > RGLRU_MAX_TAPS) return (int)cudaErrorInvalidValue;
   OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(rglru_scan_kernel<T>, dim3((C + 31) / 32, num_seqs), dim3(32 * warps), 0, stream, a,
                                           b, y, C, K, S_state, conv_state, (const T*)proj, stride, x_col, x_bias, cu_seqlens,
+                                          state_slots, (T*)out)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// A step of single tokens (cu_seqlens[i + 1] - cu_seqlens[i] is 1, or 0 for a request that sits out):
+// everything in one kernel. gates float32 [blocks, bw, 2 bw].
+extern "C" int omnia_rglru_step(const void* proj, int stride, int x_col, int y_col, const float* x_bias, const float* y_bias,
+                                const float* taps, const float* conv_bias, const float* gates, const float* r_bias,
+                                const float* i_bias, const float* lam, float c_decay, int C, int bw, int K, float* S_state,
+                                float* conv_state, const int* cu_seqlens, const int* state_slots, int num_seqs, void* out,
+                                int dtype, cudaStream_t stream) {
+  if (num_seqs == 0) return 0;
+  if (bw < 1 || C % bw || K < 1 || K > RGLRU_MAX_TAPS || 3 * bw * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
+  const int threads = 2 * bw >= 256 ? 256 : (2 * bw + 31) / 32 * 32;
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(rglru_step_kernel<T>, dim3(C / bw, num_seqs), dim3(threads), 3 * bw * sizeof(float),
+                                          stream, (const T*)proj, stride, x_col, y_col, x_bias, y_bias, taps, conv_bias, gates,
+                                          r_bias, i_bias, lam, c_decay, C, bw, K, S_state, conv_state, cu_seqlens,
                                           state_slots, (T*)out)));
   return OMNIA_LAUNCH_RESULT();
 }

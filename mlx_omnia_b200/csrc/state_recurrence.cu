@@ -13,9 +13,11 @@
 //               Out: one float32 row a token, [q | k | v | a], every section starting on 16 bytes.
 //   recurrence  sequential in a request's tokens, parallel over (request, head, run of value columns):
 //               the columns of S are independent. A column is held by P threads, each with DK / P of
-//               its rows in registers. The next STATE_CHUNK tokens' q, k, (a) and v are brought into
-//               the other half of a double buffer by asynchronous 16-byte copies while these are walked;
-//               they arrive in the layout the column threads read, so nothing is converted on the way.
+//               its rows in registers. The block's last STATE_LOADERS threads are loaders: while the
+//               column threads walk one run of STATE_CHUNK tokens, the loaders bring the next run's q, k,
+//               (a) and v into the other half of a double buffer by asynchronous 16-byte copies; the rows
+//               arrive in the layout the column threads read, so nothing is converted on the way, and the
+//               column threads issue nothing but the recurrence. One barrier a run.
 //               A token's partial sums stay in registers until the run is done: the chain from token to
 //               token is one multiply and one fused multiply-add a row. The arithmetic of a token does
 //               not depend on how the tokens were cut into steps.
@@ -30,7 +32,8 @@
 #define STATE_DK 64
 #endif
 #define STATE_CHUNK 16     // tokens staged in shared memory at a time
-#define STATE_THREADS 512  // of a block at most
+#define STATE_THREADS 512  // column threads of a block at most
+#define STATE_LOADERS 64   // threads of a block that stage the next tokens while the others walk these
 
 namespace {
 
@@ -80,8 +83,9 @@ __global__ void state_inputs_kernel(const T* __restrict__ proj, int stride, int 
 
 // CHANNEL: a decay per token and key channel (section a of the rows); else the head's constant.
 template <int P, bool CHANNEL>
-__global__ void __launch_bounds__(STATE_THREADS) state_recurrence_kernel(
-    const float* __restrict__ rows, int row_floats, int H, int dv, int cols, int parts, const float* __restrict__ decay,
+__global__ void __launch_bounds__(STATE_THREADS + STATE_LOADERS) state_recurrence_kernel(
+    const float* __restrict__ rows, int row_floats, int H, int dv, int cols, int parts, int column_threads,
+    const float* __restrict__ decay,
     float* __restrict__ S_state, const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
     float* __restrict__ o_raw) {
   pdl_wait();
@@ -103,8 +107,10 @@ __global__ void __launch_bounds__(STATE_THREADS) state_recurrence_kernel(
   const int col0 = part * cols;
   const int begin = cu_seqlens[seq], end = cu_seqlens[seq + 1];
   if (end <= begin) return;
+  const bool loader = (int)threadIdx.x >= column_threads;
+  const int loaders = (int)blockDim.x - column_threads, lt = (int)threadIdx.x - column_threads;
   const int j = threadIdx.x / P, p = threadIdx.x % P;
-  const bool live = j < cols && col0 + j < dv;
+  const bool live = !loader && j < cols && col0 + j < dv;
   const float lambda = CHANNEL ? 1.f : decay[head];
   const int qk = H * DK, k_at = pad4(qk), v_at = 2 * pad4(qk), a_at = v_at + pad4(H * dv);
   // Whole 16-byte pieces from starts on 16 bytes: the asynchronous way.
@@ -115,30 +121,34 @@ __global__ void __launch_bounds__(STATE_THREADS) state_recurrence_kernel(
   auto section = [&](int which) { return which == 0 ? 0 : which == 1 ? k_at : a_at; };
   auto fetch = [&](int t0, int n, float* buf) {
     if (wide) {
-      for (int item = threadIdx.x; item < n * per_token; item += blockDim.x) {
-        const int tok = item / per_token, r = item % per_token;
+      // Item = token * per_token + piece; token and piece are kept up step by step (no division by a
+      // number that only the launch knows inside the loop).
+      int tok = lt / per_token, piece = lt % per_token;
+      for (int item = lt; item < n * per_token; item += loaders) {
         const float* row = rows + (size_t)(t0 + tok) * row_floats;
         const float* src;
         float* dst;
-        if (r < VECS * PIECES) {
-          const int which = r / PIECES, i0 = (r % PIECES) * 4;
+        bool past = false;
+        if (piece < VECS * PIECES) {
+          const int which = piece / PIECES, i0 = (piece % PIECES) * 4;
           src = row + section(which) + head * DK + i0;
           dst = buf + (which * TC + tok) * VROW + (i0 / R) * SEG + i0 % R;
         } else {
-          const int c = (r - VECS * PIECES) * 4;
+          const int c = (piece - VECS * PIECES) * 4;
           src = row + v_at + head * dv + col0 + c;
           dst = buf + VECS * TC * VROW + tok * vcols + c;
-          if (col0 + c >= dv) {  // past the head's last column (its last run of columns is a short one)
-            *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
-            continue;
-          }
+          past = col0 + c >= dv;  // past the head's last column (its last run of columns is a short one)
         }
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
-                     : "memory");
+        if (past) *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+        else
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                       : "memory");
+        piece += loaders;
+        while (piece >= per_token) piece -= per_token, ++tok;
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     } else {
-      for (int idx = threadIdx.x; idx < n * DK; idx += blockDim.x) {
+      for (int idx = lt; idx < n * DK; idx += loaders) {
         const int tok = idx / DK, i = idx % DK;
         const float* row = rows + (size_t)(t0 + tok) * row_floats + head * DK + i;
         const int at = tok * VROW + (i / R) * SEG + i % R;
@@ -146,7 +156,7 @@ __global__ void __launch_bounds__(STATE_THREADS) state_recurrence_kernel(
         buf[TC * VROW + at] = row[k_at];
         if (CHANNEL) buf[2 * TC * VROW + at] = row[a_at];
       }
-      for (int idx = threadIdx.x; idx < n * cols; idx += blockDim.x) {
+      for (int idx = lt; idx < n * cols; idx += loaders) {
         const int tok = idx / cols, c = idx % cols;
         buf[VECS * TC * VROW + tok * vcols + c] =
             col0 + c < dv ? rows[(size_t)(t0 + tok) * row_floats + v_at + head * dv + col0 + c] : 0.f;
@@ -163,13 +173,16 @@ __global__ void __launch_bounds__(STATE_THREADS) state_recurrence_kernel(
   }
 
   const int runs = (end - begin + TC - 1) / TC;
-  fetch(begin, min(TC, end - begin), shared);
+  if (loader) fetch(begin, min(TC, end - begin), shared);
   for (int c = 0; c < runs; ++c) {
     const int t0 = begin + c * TC;
     const int n = min(TC, end - t0);
-    if (wide) asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();  // this run has arrived for everybody; the other half has been read
-    if (c + 1 < runs) fetch(t0 + TC, min(TC, end - t0 - TC), shared + ((c + 1) & 1) * half);
+    if (loader && wide) asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // this run has arrived; the other half has been read
+    if (loader) {
+      if (c + 1 < runs) fetch(t0 + TC, min(TC, end - t0 - TC), shared + ((c + 1) & 1) * half);
+      continue;
+    }
     const float* qs = shared + (c & 1) * half;
     const float* ks = qs + TC * VROW;
     const float* as = ks + TC * VROW;
@@ -285,10 +298,11 @@ extern "C" int omnia_state_max_cols(void) {
 
 // rows: the prepared rows; channel != 0: they carry a decay per key channel, else decay float32 [H].
 // S_state float32 [slots, H, DK, dv], updated in place; o_raw float32 [tokens, H * dv]. cols: value
-// columns a block takes (a head is cut into ceil(dv / cols) runs; at most omnia_state_max_cols()).
+// columns a block takes (a head is cut into ceil(dv / cols) runs; at most omnia_state_max_cols());
+// column_team: threads a column (1, 2, 4, 8 or 16; 0: chosen here).
 extern "C" int omnia_state_recurrence(const float* rows, int H, int dv, int cols, int channel, const float* decay,
                                       float* S_state, const int* cu_seqlens, const int* state_slots, int num_seqs,
-                                      float* o_raw, cudaStream_t stream) {
+                                      float* o_raw, int column_team, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (H < 1 || dv < 1 || cols < 1 || cols > omnia_state_max_cols() || (!channel && decay == nullptr))
     return (int)cudaErrorInvalidValue;
@@ -303,8 +317,10 @@ extern "C" int omnia_state_recurrence(const float* rows, int H, int dv, int cols
     if (smem > 48 * 1024 && cudaFuncSetAttribute(state_recurrence_kernel<P, CHANNEL>,                           \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
       return (int)cudaGetLastError();                                                                           \
-    launch_pdl(state_recurrence_kernel<P, CHANNEL>, grid, dim3((cols * P + 31) / 32 * 32), smem, stream, rows,   \
-               row_floats, H, dv, cols, parts, decay, S_state, cu_seqlens, state_slots, o_raw);                 \
+    const int column_threads = (cols * P + 31) / 32 * 32;                                                       \
+    launch_pdl(state_recurrence_kernel<P, CHANNEL>, grid, dim3(column_threads + STATE_LOADERS), smem, stream,    \
+               rows, row_floats, H, dv, cols, parts, column_threads, decay, S_state, cu_seqlens, state_slots,   \
+               o_raw);                                                                                          \
   } while (0)
 #define OMNIA_STATE_LAUNCH(P)                                   \
   do {                                                          \
@@ -315,12 +331,23 @@ extern "C" int omnia_state_recurrence(const float* rows, int H, int dv, int cols
       return (int)cudaErrorInvalidValue;                        \
     }                                                           \
   } while (0)
-  // Threads a column: as many as leave each at least four rows of S and fit the block.
-  if (cols * 16 <= STATE_THREADS && STATE_DK >= 64) OMNIA_STATE_LAUNCH(16);
-  else if (cols * 8 <= STATE_THREADS && STATE_DK >= 32) OMNIA_STATE_LAUNCH(8);
-  else if (cols * 4 <= STATE_THREADS && STATE_DK >= 16) OMNIA_STATE_LAUNCH(4);
-  else if (cols * 2 <= STATE_THREADS && STATE_DK >= 8) OMNIA_STATE_LAUNCH(2);
-  else if (cols <= STATE_THREADS) OMNIA_STATE_LAUNCH(1);
+  // Threads a column (column_team, when the caller names it): as many as give each sixteen rows of S
+  // (measured on B200 at key widths of 64 and 128: teams of 4 and 8 walk a prompt a quarter faster
+  // than teams of 16; a team's threads read the same q, k and decays as every other column's team, so
+  // fewer and longer threads ask shared memory for less), and no more than fit the block.
+  if (column_team > 0 && (cols * column_team > STATE_THREADS || column_team > STATE_DK)) return (int)cudaErrorInvalidValue;
+  int team = column_team;
+  if (team <= 0) {
+    team = 1;
+    while (team < 16 && STATE_DK / (2 * team) >= 16) team *= 2;
+    while ((STATE_DK + team - 1) / team > 32) team *= 2;
+    while (team > 1 && cols * team > STATE_THREADS) team /= 2;
+  }
+  if (team == 16) OMNIA_STATE_LAUNCH(16);
+  else if (team == 8) OMNIA_STATE_LAUNCH(8);
+  else if (team == 4) OMNIA_STATE_LAUNCH(4);
+  else if (team == 2) OMNIA_STATE_LAUNCH(2);
+  else if (team == 1 && cols <= STATE_THREADS) OMNIA_STATE_LAUNCH(1);
   else return (int)cudaErrorInvalidValue;
 #undef OMNIA_STATE_LAUNCH
 #undef OMNIA_STATE_LAUNCH_AS

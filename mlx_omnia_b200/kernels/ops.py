@@ -1010,6 +1010,18 @@ def linear(a, weight: torch.Tensor) -> torch.Tensor:
     return _library_mm(a, weight)
 
 
+def linear_add(a: torch.Tensor, weight: torch.Tensor, alpha: float, other: torch.Tensor, beta: float) -> torch.Tensor:
+    """alpha * (a @ weight^T) + beta * other -> [rows, n], the sum taken on the product's float32
+    accumulators and rounded once: the vendor library's product with both constants in its epilogue. A
+    few bfloat16 rows run on the weight-streaming kernel and meet `other` in a pass of their own."""
+    if _skinny(a, weight):
+        return scaled_sum(linear(a, weight), alpha, other, beta)
+    if a.dtype == torch.float32 and (torch.backends.cuda.matmul.allow_tf32
+                                      or torch.get_float32_matmul_precision() != "highest"):
+        raise KernelError("the 32-bit path needs true float32 matrix products; TF32 is switched on")
+    return torch.addmm(other, a, weight.t(), beta=beta, alpha=alpha)
+
+
 def linear_swiglu(a, gate_up: torch.Tensor) -> torch.Tensor:
     """silu(a @ gate^T) * (a @ up^T) with gate_up = [gate rows | up rows] -> [rows, inner].
     `a` may be a PendingStep."""
@@ -1330,18 +1342,19 @@ def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float) -> torch.
 
 
 def state_columns(requests: int, heads: int, dk: int, dv: int, sms: int) -> int:
-    """How many of a head's value columns a block of the recurrence kernel takes: at most 96 (four
-    threads a column then fit a block) and no more than the key width leaves room for (a column needs
-    enough threads that each holds at most 32 rows of the state); in fours where dv comes in fours; and
-    halved, down to 16, while (request, head, run of columns) triples leave a quarter of the SMs idle."""
+    """How many of a head's value columns a block of the recurrence kernel takes: at most 96 and no
+    more than the key width leaves room for (a column needs enough threads that each holds at most 32
+    rows of the state); a divisor of dv where it has one in reach, in fours where dv comes in fours; and
+    halved, down to 8, while (request, head, run of columns) triples leave a quarter of the SMs idle: a
+    prompt's tokens are walked one after another, so a lone prompt wants many narrow blocks."""
     threads = 1
     while -(-dk // threads) > 32:
         threads *= 2
-    most = min(96, 512 // threads)
-    cols = min(dv, most)
+    most = min(96, 512 // threads, dv)
+    cols = next((c for c in range(most, most // 2, -1) if dv % c == 0 and (dv % 4 or c % 4 == 0)), most)
     if dv % 4 == 0:
         cols = max(4, cols // 4 * 4)
-    while cols >= 32 and requests * heads * -(-dv // cols) < sms - sms // 4:
+    while cols >= 16 and requests * heads * -(-dv // cols) < sms - sms // 4:
         cols = -(-cols // 2)
         if dv % 4 == 0:
             cols = -(-cols // 4) * 4
@@ -1353,7 +1366,7 @@ def state_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gate
                     decay_logits: torch.Tensor | None = None, decay_bias: torch.Tensor | None = None, tau: float = 1.0,
                     inv_freq: torch.Tensor | None = None, q_scale: float = 1.0, k_scale: float = 1.0,
                     norm_weight: torch.Tensor | None = None, gate: str = "silu",
-                    cols: int | None = None) -> torch.Tensor:
+                    cols: int | None = None, team: int = 0) -> torch.Tensor:
     """Linear attention over this step's tokens, request by request from the state in `S`
     [slots, heads, dk, dv] (float32, updated in place): per head S <- diag(a) S + k v^T, o = S^T q.
     q, k (heads * dk each) and v (heads * dv) are columns of the projected rows `proj`; q and k are
@@ -1363,7 +1376,8 @@ def state_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gate
     `decay_logits` [tokens, heads * dk], a = sigmoid(logits + decay_bias)^(1 / tau) per token and key
     channel. Every head's o is divided by its own root mean square (`eps` inside the root), multiplied
     by `norm_weight` ([dv], shared by the heads; None: no weight) and by silu or sigmoid (`gate`) of the
-    columns from gate_col. `cols`: value columns a block takes. -> [tokens, heads * dv]"""
+    columns from gate_col. `cols`: value columns a block takes; `team`: threads a column (0: the kernel's
+    choice). -> [tokens, heads * dv]"""
     tokens, stride = proj.shape
     if (decay is None) == (decay_logits is None):
         raise KernelError("state_attention takes either a decay per head or decay logits per token")
@@ -1386,9 +1400,9 @@ def state_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gate
     o_raw = torch.empty(tokens, width, dtype=torch.float32, device=proj.device)
     fn = _function("state_recurrence", "omnia_state_recurrence",
                    [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                    c_void_p], defines)
+                    c_int, c_void_p], defines)
     _check(fn(_ptr(rows), heads, dv, cols, int(channel), _ptr(decay), _ptr(S), _ptr(step.cu_seqlens),
-              _ptr(step.state_slots), step.num_seqs, _ptr(o_raw), _stream()), "state_recurrence")
+              _ptr(step.state_slots), step.num_seqs, _ptr(o_raw), team, _stream()), "state_recurrence")
     out = torch.empty(tokens, width, dtype=proj.dtype, device=proj.device)
     fn = _function("state_recurrence", "omnia_state_heads_out",
                    [c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
@@ -1424,6 +1438,17 @@ def gated_channel_recurrence(proj: torch.Tensor, x_col: int, y_col: int, x_bias:
     if blocks * bw != C or gates.shape[2] != 2 * bw or not 1 <= K <= RGLRU_MAX_TAPS:
         raise KernelError(f"a recurrence over {C} channels in {blocks} blocks of {bw}, {K} taps")
     device, code = proj.device, _code(proj.dtype)
+    if step.decode_only and 3 * bw * 4 <= 48 * 1024:
+        # Single tokens: the convolution, the gates' maps and the recurrence in one kernel.
+        out = torch.empty(tokens, C, dtype=proj.dtype, device=device)
+        fn = _function("rglru", "omnia_rglru_step",
+                       [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                        c_void_p])
+        _check(fn(_ptr(proj), stride, x_col, y_col, _ptr(x_bias), _ptr(y_bias), _ptr(taps), _ptr(conv_bias), _ptr(gates),
+                  _ptr(r_bias), _ptr(i_bias), _ptr(lam), c_decay, C, bw, K, _ptr(S), _ptr(conv_state), _ptr(step.cu_seqlens),
+                  _ptr(step.state_slots), step.num_seqs, _ptr(out), code, _stream()), "rglru_step")
+        return out
     u = torch.empty(tokens, C, dtype=torch.float32, device=device)
     fn = _function("rglru", "omnia_rglru_conv",
                    [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,

@@ -325,15 +325,21 @@ class SinkWindowAttention(Mixer):
         self.o = tensors["o"].contiguous()
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        return ops.linear(self.forward_heads(ops.linear(h, self.in_proj), 0, ctx), self.o)
+
+    def forward_heads(self, proj: torch.Tensor, col0: int, ctx) -> torch.Tensor:
+        """The heads' outputs side by side, ahead of the output projection, from projected rows whose
+        columns from `col0` on are this mixer's input projection (a mixer that runs several side by side
+        makes their input projections in one product)."""
         if ctx.kv is None:
             raise RuntimeError("an attention mixer needs cache pages")
         if ctx.kv.writes and not self.own_kv:
             raise RuntimeError("a mixer without k/v projections cannot own a cache entry")
-        proj = ops.linear(h, self.in_proj)
-        q = ops.qkv_prepare(proj, 0, self.k_col, self.v_col, self.heads, self.dim, self.in_bias, self.q_norm,
+        if col0 and self.in_bias is not None:
+            raise RuntimeError("biased projections start at the projected rows' first column")
+        q = ops.qkv_prepare(proj, col0, col0 + self.k_col, col0 + self.v_col, self.heads, self.dim, self.in_bias, self.q_norm,
                             self.k_norm, self.norm_eps, self.position.table(), ctx.step.positions, ctx.kv,
                             store=self.own_kv, whole=self.norm_over == "projection", interleaved=self.interleaved)
-        out = ops.paged_attention(q, ctx.kv, ctx.step, self.scale, gate=proj if self.gated else None,
-                                  gate_col=self.gate_col, sink=self.sink_logits, window=self.window,
-                                  keep_first=self.keep_first, chunk=self.chunk, softcap=self.softcap)
-        return ops.linear(out, self.o)
+        return ops.paged_attention(q, ctx.kv, ctx.step, self.scale, gate=proj if self.gated else None,
+                                   gate_col=col0 + self.gate_col, sink=self.sink_logits, window=self.window,
+                                   keep_first=self.keep_first, chunk=self.chunk, softcap=self.softcap)

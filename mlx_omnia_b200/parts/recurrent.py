@@ -239,15 +239,19 @@ class GatedStateAttention(Mixer):
             self.a2, self.a2_bias = tensors["a2"].contiguous(), tensors["a2.b"].contiguous()
 
     def forward(self, h, ctx) -> torch.Tensor:
-        proj = ops.linear(h, self.in_proj)
+        return ops.linear(self.forward_heads(ops.linear(h, self.in_proj), 0, ctx), self.o)
+
+    def forward_heads(self, proj: torch.Tensor, col0: int, ctx) -> torch.Tensor:
+        """The heads' gated outputs side by side, ahead of the output projection, from projected rows
+        whose columns from `col0` on are this mixer's input projection."""
         logits = None
         if self.decay is None:
-            logits = ops.linear(proj[:, self.a1_col: self.a1_col + self.decay_rank], self.a2)
-        out = ops.state_attention(proj, 0, self.k_col, self.v_col, self.gate_col, self.heads, self.dim, self.vdim,
-                                  ctx.state, ctx.step, self.norm_eps, decay=self.decays, decay_logits=logits,
-                                  decay_bias=self.a2_bias, tau=self.tau, inv_freq=self.position.table(),
-                                  q_scale=self.q_scale, k_scale=self.k_scale, norm_weight=self.norm, gate=self.gate)
-        return ops.linear(out, self.o)
+            logits = ops.linear(proj[:, col0 + self.a1_col: col0 + self.a1_col + self.decay_rank], self.a2)
+        return ops.state_attention(proj, col0, col0 + self.k_col, col0 + self.v_col, col0 + self.gate_col, self.heads,
+                                   self.dim, self.vdim, ctx.state, ctx.step, self.norm_eps, decay=self.decays,
+                                   decay_logits=logits, decay_bias=self.a2_bias, tau=self.tau,
+                                   inv_freq=self.position.table(), q_scale=self.q_scale, k_scale=self.k_scale,
+                                   norm_weight=self.norm, gate=self.gate)
 
 
 @register_mixer("gated_channel_recurrence")
@@ -301,12 +305,17 @@ class GatedChannelRecurrence(Mixer):
         self.r_bias, self.i_bias = tensors["ra.b"].reshape(-1).contiguous(), tensors["ri.b"].reshape(-1).contiguous()
         self.lam, self.o = tensors["lam"].contiguous(), tensors["o"].contiguous()
 
+    takes_pending = True  # h goes to the in-projection and nowhere else
+
     def forward(self, h, ctx) -> torch.Tensor:
-        proj = ops.linear(h, self.in_proj)
-        out = ops.gated_channel_recurrence(proj, 0, self.width, self.x_bias, self.y_bias, self.taps, self.conv_bias,
-                                           self.gates, self.r_bias, self.i_bias, self.lam, self.c_decay, ctx.state["S"],
-                                           ctx.state["conv"], ctx.step)
-        return ops.linear(out, self.o)
+        return ops.linear(self.forward_heads(ops.linear(h, self.in_proj), 0, ctx), self.o)
+
+    def forward_heads(self, proj: torch.Tensor, col0: int, ctx) -> torch.Tensor:
+        """S * y for every channel, ahead of the output projection, from projected rows whose columns
+        from `col0` on are this mixer's input projection."""
+        return ops.gated_channel_recurrence(proj, col0, col0 + self.width, self.x_bias, self.y_bias, self.taps,
+                                            self.conv_bias, self.gates, self.r_bias, self.i_bias, self.lam, self.c_decay,
+                                            ctx.state["S"], ctx.state["conv"], ctx.step)
 
 
 @register_mixer("side_by_side")
@@ -316,7 +325,12 @@ class SideBySide(Mixer):
 
     left, right: PartSpecs of registered mixers; their tensors sit under `left.` and `right.`. At most
     one of the two may keep rows in the paged cache (the schedule entry's pages are that one's); each
-    may keep per-request state, which this part hands to its owner."""
+    may keep per-request state, which this part hands to its owner.
+
+    Two sides that each are an input projection `in_proj`, a `forward_heads(projected rows, first
+    column, ctx)` and an output projection `o` run as one input product over both sides' stacked rows
+    (so the mixer may take a pending residual step), and the left side's output product takes the
+    right side's result and both constants in its epilogue; any other pair runs side by side as it is."""
 
     def __init__(self, left: PartSpec, right: PartSpec, left_scale: float = 1.0, right_scale: float = 1.0) -> None:
         self.sides = {"left": MIXERS.build(left), "right": MIXERS.build(right)}
@@ -353,6 +367,20 @@ class SideBySide(Mixer):
         for name, side in self.sides.items():
             prefix = name + "."
             side.load({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, runtime)
+        left, right = self.sides["left"], self.sides["right"]
+        self.fused = all(hasattr(side, "forward_heads") and hasattr(side, "in_proj") and hasattr(side, "o")
+                         and getattr(side, "in_bias", None) is None and side.in_proj.shape[0] % 8 == 0
+                         for side in (left, right))
+        self.takes_pending = self.fused  # h then goes to the one input product and nowhere else
+        if self.fused:
+            self.in_proj = torch.cat([left.in_proj, right.in_proj], dim=0).contiguous()
+            self.right_col = left.in_proj.shape[0]
+            left.in_proj, right.in_proj = self.in_proj[: self.right_col], self.in_proj[self.right_col:]
+
+    def _context(self, name: str, ctx) -> LayerContext:
+        side = self.sides[name]
+        return LayerContext(ctx.step, ctx.kv if side.kv_spec() is not None else None, self._state_of(name, ctx.state),
+                            ctx.entry, ctx.block_state, False)
 
     def _state_of(self, name: str, state):
         if name not in self._stateful:
@@ -365,9 +393,11 @@ class SideBySide(Mixer):
         return state[name]
 
     def forward(self, h, ctx) -> torch.Tensor:
-        outs = {}
-        for name, side in self.sides.items():
-            mine = LayerContext(ctx.step, ctx.kv if side.kv_spec() is not None else None, self._state_of(name, ctx.state),
-                                ctx.entry, ctx.block_state, False)
-            outs[name] = side.forward(h, mine)
-        return ops.scaled_sum(outs["left"], self.scales["left"], outs["right"], self.scales["right"])
+        left, right = self.sides["left"], self.sides["right"]
+        if not self.fused:
+            outs = {name: side.forward(ops.settle(h), self._context(name, ctx)) for name, side in self.sides.items()}
+            return ops.scaled_sum(outs["left"], self.scales["left"], outs["right"], self.scales["right"])
+        proj = ops.linear(h, self.in_proj)
+        mixed_right = ops.linear(right.forward_heads(proj, self.right_col, self._context("right", ctx)), right.o)
+        return ops.linear_add(left.forward_heads(proj, 0, self._context("left", ctx)), left.o, self.scales["left"],
+                              mixed_right, self.scales["right"])

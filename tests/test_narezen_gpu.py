@@ -137,11 +137,12 @@ def test_a_far_token_shows_through_a_slow_decay_and_not_through_a_fast_one():
 @pytest.mark.parametrize("C,blocks,K", [(48, 3, 3), (64, 1, 1), (30, 5, 5), (160, 2, 4), (512, 4, 16)])
 def test_gated_channel_recurrence_over_portions_and_slots(dtype, C, blocks, K):
     """Two requests in portions of 1 to 700 tokens (shorter than the convolution's reach, and long
-    enough for the scan to be cut into segments) from slots that others used before."""
+    enough for the scan to be cut into segments) from slots that others used before, then six steps of
+    one token each (the kernel that does a decoding step in one launch)."""
     g = torch.Generator().manual_seed(C + K)
     dt = DTYPES[dtype]
     bw = C // blocks
-    Ta, Tb = 790, 41
+    Ta, Tb = 796, 47
     rows = {r: (torch.randn(T, 2 * C + 3, generator=g)).to(dt) for r, T in (("a", Ta), ("b", Tb))}
     W = {"x.b": torch.randn(C, generator=g) * 0.3, "y.b": torch.randn(C, generator=g) * 0.3,
          "conv": torch.randn(C, K, generator=g) * K ** -0.5, "conv.b": torch.randn(C, generator=g) * 0.1,
@@ -155,8 +156,8 @@ def test_gated_channel_recurrence_over_portions_and_slots(dtype, C, blocks, K):
     S[[3, 1]] = 0.0
     conv[[3, 1]] = 0.0
     got = {"a": [], "b": []}
-    cuts = {"a": [0, 37, 38, 40, 56, 75, 775, 790], "b": [0, 1, 2, 3, 19, 20, 21, 41]}
-    for i in range(7):
+    cuts = {"a": [0, 37, 38, 40, 56, 75, 775, 790] + list(range(791, 797)), "b": [0, 1, 2, 3, 19, 20, 21, 41] + list(range(42, 48))}
+    for i in range(13):
         a0, a1, b0, b1 = cuts["a"][i], cuts["a"][i + 1], cuts["b"][i], cuts["b"][i + 1]
         step = Batch([a1 - a0, b1 - b0], [a0, b0], [3, 1])
         proj = torch.cat([rows["a"][a0:a1], rows["b"][b0:b1]]).to(CUDA)
@@ -288,7 +289,7 @@ def engine_for(name, dtype="float32", page=4, tokens=1024, requests=4, graphs=Tr
     return raw, weights, engine
 
 
-TOLERANCE = {"float32": 3e-4, "bfloat16": 6e-2}
+TOLERANCE = {"float32": 3e-4, "bfloat16": 8e-2}
 
 
 def every_expert(raw) -> bool:
