@@ -458,6 +458,37 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const T* __restri
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const bool wide = hidden % VEC == 0 && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)h & 15) == 0 &&
+                    ((uintptr_t)y & 15) == 0 && ((uintptr_t)extra & 15) == 0;
+  if (wide) {
+    // Sixteen bytes of every row at a time; a choice's place and weight are read once per piece.
+    for (int i = threadIdx.x * VEC; i < hidden; i += blockDim.x * VEC) {
+      float acc[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+      for (int k = 0; k < top; ++k) {
+        const int p = place[(size_t)t * top + k];
+        const float w = weight ? weight[(size_t)t * top + k] : 1.f;
+        const uint4 piece = *reinterpret_cast<const uint4*>((p >= 0 ? rows + (size_t)p * hidden : h + (size_t)t * hidden) + i);
+        const T* v = reinterpret_cast<const T*>(&piece);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] += weight ? w * to_f32(v[e]) : to_f32(v[e]);
+      }
+      if (extra) {
+        const uint4 piece = *reinterpret_cast<const uint4*>(extra + (size_t)t * hidden + i);
+        const T* v = reinterpret_cast<const T*>(&piece);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] += to_f32(v[e]);
+      }
+      uint4 out;
+      T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) o[e] = from_f32<T>(acc[e]);
+      *reinterpret_cast<uint4*>(y + (size_t)t * hidden + i) = out;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -633,6 +664,19 @@ __global__ void moe_weighted_rows_kernel(const T* __restrict__ h, const int* __r
   const float w = weight[pair];
   const T* src = h + (size_t)(pair / top) * hidden;
   T* dst = rows + (size_t)r * hidden;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  if (hidden % VEC == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)rows & 15) == 0) {
+    for (int i = threadIdx.x * VEC; i < hidden; i += blockDim.x * VEC) {
+      const uint4 piece = *reinterpret_cast<const uint4*>(src + i);
+      const T* v = reinterpret_cast<const T*>(&piece);
+      uint4 out;
+      T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) o[e] = from_f32<T>(w * to_f32(v[e]));
+      *reinterpret_cast<uint4*>(dst + i) = out;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>(w * to_f32(src[i]));
 }
 

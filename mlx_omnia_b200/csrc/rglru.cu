@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(32 * RGLRU_SCAN_WARPS) rglru_scan_kernel(
 
 // grid (blocks of the maps, requests); gates [blocks, bw (in), 2 bw (out: r's, then i's)].
 template <typename T>
-__global__ void __launch_bounds__(256) rglru_step_kernel(
+__global__ void __launch_bounds__(1024) rglru_step_kernel(
     const T* __restrict__ proj, int stride, int x_col, int y_col, const float* __restrict__ x_bias,
     const float* __restrict__ y_bias, const float* __restrict__ taps, const float* __restrict__ conv_bias,
     const float* __restrict__ gates, const float* __restrict__ r_bias, const float* __restrict__ i_bias,
@@ -169,9 +169,10 @@ __global__ void __launch_bounds__(256) rglru_step_kernel(
     T* __restrict__ out) {
   pdl_wait();
   pdl_launch_dependents();
-  extern __shared__ float step_s[];  // u [bw] | z [2 bw]
+  extern __shared__ float step_s[];  // u [bw] | z [2 bw] | partial sums [teams][2 bw]
   float* u_s = step_s;
   float* z_s = step_s + bw;
+  float* part_s = step_s + 3 * bw;
   const int block = blockIdx.x, seq = blockIdx.y;
   const int t = cu_seqlens[seq];
   if (cu_seqlens[seq + 1] <= t) return;
@@ -190,11 +191,25 @@ __global__ void __launch_bounds__(256) rglru_step_kernel(
     u_s[o] = acc;
   }
   __syncthreads();
+  // The maps' products: `teams` threads an output, each over a run of the inputs; the runs' sums are
+  // added in their order (the block's size fixes the runs, so a step's arithmetic never depends on
+  // which requests it holds).
   const float* g = gates + (size_t)block * bw * 2 * bw;
-  for (int o = threadIdx.x; o < 2 * bw; o += blockDim.x) {
+  const int outputs = 2 * bw;
+  const int teams = (int)blockDim.x / outputs > 0 ? (int)blockDim.x / outputs : 1;
+  const int per = (bw + teams - 1) / teams;
+  for (int item = threadIdx.x; item < teams * outputs; item += blockDim.x) {
+    const int team = item / outputs, o = item % outputs;
+    const int i0 = team * per, i1 = min(bw, i0 + per);
     float acc = 0.f;
 #pragma unroll 8
-    for (int i = 0; i < bw; ++i) acc = fmaf(g[(size_t)i * 2 * bw + o], u_s[i], acc);
+    for (int i = i0; i < i1; ++i) acc = fmaf(g[(size_t)i * outputs + o], u_s[i], acc);
+    part_s[team * outputs + o] = acc;
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < outputs; o += blockDim.x) {
+    float acc = 0.f;
+    for (int team = 0; team < teams; ++team) acc += part_s[team * outputs + o];
     z_s[o] = acc;
   }
   __syncthreads();
@@ -265,9 +280,14 @@ extern "C" int omnia_rglru_step(const void* proj, int stride, int x_col, int y_c
                                 float* conv_state, const int* cu_seqlens, const int* state_slots, int num_seqs, void* out,
                                 int dtype, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
-  if (bw < 1 || C % bw || K < 1 || K > RGLRU_MAX_TAPS || 3 * bw * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
-  const int threads = 2 * bw >= 256 ? 256 : (2 * bw + 31) / 32 * 32;
-  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(rglru_step_kernel<T>, dim3(C / bw, num_seqs), dim3(threads), 3 * bw * sizeof(float),
+  if (bw < 1 || C % bw || K < 1 || K > RGLRU_MAX_TAPS || 5 * bw * sizeof(float) > 40 * 1024) return (int)cudaErrorInvalidValue;
+  // Up to eight threads an output of the maps (the products are latency, not arithmetic), 1024 at most.
+  int threads = (2 * bw + 31) / 32 * 32;
+  if (threads < 1024) threads = threads * 8 <= 1024 ? threads * 8 : 1024 / (2 * bw) > 0 ? 1024 / (2 * bw) * 2 * bw : 1024;
+  threads = (threads + 31) / 32 * 32 > 1024 ? 1024 : (threads + 31) / 32 * 32;
+  const int teams = threads / (2 * bw) > 0 ? threads / (2 * bw) : 1;
+  const size_t smem = (size_t)(3 * bw + teams * 2 * bw) * sizeof(float);
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(rglru_step_kernel<T>, dim3(C / bw, num_seqs), dim3(threads), smem,
                                           stream, (const T*)proj, stride, x_col, y_col, x_bias, y_bias, taps, conv_bias, gates,
                                           r_bias, i_bias, lam, c_decay, C, bw, K, S_state, conv_state, cu_seqlens,
                                           state_slots, (T*)out)));

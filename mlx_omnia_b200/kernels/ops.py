@@ -1438,7 +1438,7 @@ def gated_channel_recurrence(proj: torch.Tensor, x_col: int, y_col: int, x_bias:
     if blocks * bw != C or gates.shape[2] != 2 * bw or not 1 <= K <= RGLRU_MAX_TAPS:
         raise KernelError(f"a recurrence over {C} channels in {blocks} blocks of {bw}, {K} taps")
     device, code = proj.device, _code(proj.dtype)
-    if step.decode_only and 3 * bw * 4 <= 48 * 1024:
+    if step.decode_only and 5 * bw * 4 <= 40 * 1024:
         # Single tokens: the convolution, the gates' maps and the recurrence in one kernel.
         out = torch.empty(tokens, C, dtype=proj.dtype, device=device)
         fn = _function("rglru", "omnia_rglru_step",
