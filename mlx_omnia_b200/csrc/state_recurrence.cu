@@ -32,7 +32,7 @@
 #define STATE_DK 64
 #endif
 #define STATE_CHUNK 16     // tokens staged in shared memory at a time
-#define STATE_THREADS 512  // column threads of a block at most
+#define STATE_THREADS 448  // column threads of a block at most (with the loaders 512: 128 registers a thread)
 #define STATE_LOADERS 64   // threads of a block that stage the next tokens while the others walk these
 
 namespace {

@@ -1350,7 +1350,7 @@ def state_columns(requests: int, heads: int, dk: int, dv: int, sms: int) -> int:
     threads = 1
     while -(-dk // threads) > 32:
         threads *= 2
-    most = min(96, 512 // threads, dv)
+    most = min(96, 448 // threads, dv)
     cols = next((c for c in range(most, most // 2, -1) if dv % c == 0 and (dv % 4 or c % 4 == 0)), most)
     if dv % 4 == 0:
         cols = max(4, cols // 4 * 4)

@@ -205,6 +205,6 @@ def test_how_many_columns_a_block_of_the_recurrence_takes():
         threads = 1
         while -(-dk // threads) > 32:
             threads *= 2
-        assert 1 <= cols <= min(dv, 96) and cols * threads <= 512
+        assert 1 <= cols <= min(dv, 96) and cols * threads <= 448
         assert dv % 4 or cols % 4 == 0
     assert ops.state_columns(1, 2, 32, 64, 148) < ops.state_columns(64, 2, 32, 64, 148)  # few requests: more blocks
