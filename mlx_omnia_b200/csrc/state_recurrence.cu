@@ -9,7 +9,7 @@
 //   inputs      per token, everything that needs no other token, in float32: q and k with the first
 //               `rot` dims of every head turned in half-split pairs (i, i + rot / 2) by the angle
 //               position * inv_freq[i], then multiplied by q_scale and k_scale; v copied; with decay
-//               logits z, a = sigmoid(z + bias)^(1 / tau) = exp(log_sigmoid(z + bias) / tau).
+//               logits z (float32), a = sigmoid(z + bias)^(1 / tau) = exp(log_sigmoid(z + bias) / tau).
 //               Out: one float32 row a token, [q | k | v | a], every section starting on 16 bytes.
 //   recurrence  sequential in a request's tokens, parallel over (request, head, run of value columns):
 //               the columns of S are independent. A column is held by P threads, each with DK / P of
@@ -42,7 +42,7 @@ __device__ __forceinline__ int pad4(int n) { return (n + 3) & ~3; }
 template <typename T>
 __global__ void state_inputs_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, int v_col, int H, int dv,
                                     const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
-                                    float q_scale, float k_scale, const T* __restrict__ z, int z_stride,
+                                    float q_scale, float k_scale, const float* __restrict__ z, int z_stride,
                                     const float* __restrict__ z_bias, float inv_tau, float* __restrict__ rows,
                                     int row_floats) {
   pdl_wait();
@@ -73,7 +73,7 @@ __global__ void state_inputs_kernel(const T* __restrict__ proj, int stride, int 
     out[c] = q * q_scale;
     out[k_at + c] = k * k_scale;
     if (z != nullptr) {
-      const float x = to_f32(z[t * z_stride + c]) + (z_bias ? z_bias[c] : 0.f);
+      const float x = z[t * z_stride + c] + (z_bias ? z_bias[c] : 0.f);
       const float log_sigmoid = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
       out[a_at + c] = expf(log_sigmoid * inv_tau);
     }
@@ -273,11 +273,11 @@ extern "C" int omnia_state_row_floats(int H, int dv, int channel) {
 }
 
 // proj: projected rows [tokens, stride] with q at q_col, k at k_col (H * DK each), v at v_col (H * dv).
-// inv_freq: float32 [rot / 2] or null; z: decay logits [tokens, z_stride] (H * DK used) or null, with
+// inv_freq: float32 [rot / 2] or null; z: decay logits, float32 [tokens, z_stride] (H * DK used) or null, with
 // z_bias float32 [H * DK] or null and inv_tau = 1 / tau. rows: float32 [tokens, row_floats].
 extern "C" int omnia_state_inputs(const void* proj, int stride, int q_col, int k_col, int v_col, int H, int dv,
                                   const float* inv_freq, int rot, const int* positions, float q_scale, float k_scale,
-                                  const void* z, int z_stride, const float* z_bias, float inv_tau, float* rows,
+                                  const float* z, int z_stride, const float* z_bias, float inv_tau, float* rows,
                                   int tokens, int dtype, cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (H < 1 || dv < 1 || rot < 0 || rot > STATE_DK || rot % 2) return (int)cudaErrorInvalidValue;
@@ -285,7 +285,7 @@ extern "C" int omnia_state_inputs(const void* proj, int stride, int q_col, int k
   const int threads = H * STATE_DK >= 1024 ? 256 : 128;
   OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(state_inputs_kernel<T>, dim3(tokens), dim3(threads), 0, stream, (const T*)proj,
                                           stride, q_col, k_col, v_col, H, dv, inv_freq, rot, positions, q_scale, k_scale,
-                                          (const T*)z, z_stride, z_bias, inv_tau, rows, row_floats)));
+                                          z, z_stride, z_bias, inv_tau, rows, row_floats)));
   return OMNIA_LAUNCH_RESULT();
 }
 

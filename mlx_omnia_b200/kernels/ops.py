@@ -1373,8 +1373,8 @@ def state_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gate
     turned over the first 2 * len(inv_freq) dims of every head in half-split pairs (float32 angles from
     the step's positions) and then multiplied by q_scale and k_scale, all in float32, and enter the
     recurrence unrounded. The decay is `decay` (float32 [heads], a constant a head) or, with
-    `decay_logits` [tokens, heads * dk], a = sigmoid(logits + decay_bias)^(1 / tau) per token and key
-    channel. Every head's o is divided by its own root mean square (`eps` inside the root), multiplied
+    `decay_logits` (float32 [tokens, heads * dk]), a = sigmoid(logits + decay_bias)^(1 / tau) per token
+    and key channel. Every head's o is divided by its own root mean square (`eps` inside the root), multiplied
     by `norm_weight` ([dv], shared by the heads; None: no weight) and by silu or sigmoid (`gate`) of the
     columns from gate_col. `cols`: value columns a block takes; `team`: threads a column (0: the kernel's
     choice). -> [tokens, heads * dv]"""
@@ -1384,6 +1384,8 @@ def state_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gate
     if gate not in ("silu", "sigmoid"):
         raise KernelError(f"state_attention gates by silu or sigmoid, not {gate!r}")
     channel = decay_logits is not None
+    if channel and decay_logits.dtype != torch.float32:
+        decay_logits = decay_logits.float()
     defines = {"STATE_DK": dk}
     width = heads * dv
     if cols is None:

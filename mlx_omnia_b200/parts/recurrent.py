@@ -236,7 +236,9 @@ class GatedStateAttention(Mixer):
         if self.decay is not None:
             self.decays = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(runtime.device)
         else:
-            self.a2, self.a2_bias = tensors["a2"].contiguous(), tensors["a2.b"].contiguous()
+            # The map's second half in float32: its few inputs are the projected rows' (rounded as any
+            # projection's), its outputs, the decays' logits, are not rounded on their way into the recurrence.
+            self.a2, self.a2_bias = tensors["a2"].to(torch.float32).contiguous(), tensors["a2.b"].contiguous()
 
     def forward(self, h, ctx) -> torch.Tensor:
         return ops.linear(self.forward_heads(ops.linear(h, self.in_proj), 0, ctx), self.o)
@@ -246,7 +248,7 @@ class GatedStateAttention(Mixer):
         whose columns from `col0` on are this mixer's input projection."""
         logits = None
         if self.decay is None:
-            logits = ops.linear(proj[:, col0 + self.a1_col: col0 + self.a1_col + self.decay_rank], self.a2)
+            logits = ops.linear(proj[:, col0 + self.a1_col: col0 + self.a1_col + self.decay_rank].float(), self.a2)
         return ops.state_attention(proj, col0, col0 + self.k_col, col0 + self.v_col, col0 + self.gate_col, self.heads,
                                    self.dim, self.vdim, ctx.state, ctx.step, self.norm_eps, decay=self.decays,
                                    decay_logits=logits, decay_bias=self.a2_bias, tau=self.tau,
