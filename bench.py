@@ -1453,7 +1453,7 @@ def run_narezen(args) -> dict:
             # decays), a decay per head with rotated queries and keys, beside Bobarax's recurrence of equal heads
             lcols = 2 * R * d + 2 * R * d  # q | k | v | gate
             lproj = (torch.randn(T, lcols, device=dev) * 0.5).to(bf)
-            z = (torch.randn(T, R * d, device=dev) + 2.0).to(bf)
+            z = torch.randn(T, R * d, device=dev) + 2.0  # the decays' logits come in float32
             zb = torch.zeros(R * d, device=dev)
             S_state = torch.zeros(len(lens) + 1, R, d, d, device=dev)
             decays = torch.full((R,), 0.99, device=dev)

@@ -25,6 +25,11 @@
 //               root), times a weight [dv] that the heads share (or none), times silu or sigmoid of the
 //               gate's projected columns; rounded once to the element type.
 //
+//   step        a step in which every request brings one token (decoding) runs all three in one kernel: a
+//               block per (request, head) makes its q, k and decays, moves its whole S on (a thread a
+//               value column, or a team of threads with the rows dealt out in turn; a team's partial sums
+//               are added in the team's order), norms, gates and stores the head's output.
+//
 // Compiled per key width: -DSTATE_DK=<DK>.
 #include "common.cuh"
 
@@ -262,6 +267,84 @@ __global__ void state_heads_out_kernel(const float* __restrict__ o_raw, const T*
   }
 }
 
+// grid (heads, requests), STATE_STEP_THREADS threads. Shared: q | k | a [DK] each, partial sums
+// [teams][dv], and the block sum's scratch.
+#define STATE_STEP_THREADS 1024
+template <typename T>
+__global__ void __launch_bounds__(STATE_STEP_THREADS) state_step_kernel(
+    const T* __restrict__ proj, int stride, int q_col, int k_col, int v_col, int gate_col, int H, int dv,
+    const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions, float q_scale, float k_scale,
+    const float* __restrict__ z, int z_stride, const float* __restrict__ z_bias, float inv_tau,
+    const float* __restrict__ decay, float* __restrict__ S_state, const int* __restrict__ cu_seqlens,
+    const int* __restrict__ state_slots, const float* __restrict__ norm_w, float eps, int silu_gate, T* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
+  constexpr int DK = STATE_DK;
+  extern __shared__ float step_s[];
+  __shared__ float red[33];
+  float* q_s = step_s;
+  float* k_s = q_s + DK;
+  float* a_s = k_s + DK;
+  float* part_s = a_s + DK;  // [teams][dv]
+  const int head = blockIdx.x, seq = blockIdx.y;
+  const size_t t = cu_seqlens[seq];
+  if (cu_seqlens[seq + 1] <= (int)t) return;
+  const T* row = proj + t * stride;
+  const int half = inv_freq != nullptr ? rot / 2 : 0;
+  const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < DK; i += blockDim.x) {
+    const int c = head * DK + i;
+    float q = to_f32(row[q_col + c]), k = to_f32(row[k_col + c]);
+    if (i < 2 * half) {
+      const bool low = i < half;
+      const int f = low ? i : i - half, other = low ? c + half : c - half;
+      float sn, cs;
+      sincosf(pos * inv_freq[f], &sn, &cs);
+      const float qo = to_f32(row[q_col + other]), ko = to_f32(row[k_col + other]);
+      q = low ? q * cs - qo * sn : q * cs + qo * sn;
+      k = low ? k * cs - ko * sn : k * cs + ko * sn;
+    }
+    q_s[i] = q * q_scale;
+    k_s[i] = k * k_scale;
+    if (z != nullptr) {
+      const float x = z[t * z_stride + c] + (z_bias ? z_bias[c] : 0.f);
+      a_s[i] = expf((fminf(x, 0.f) - log1pf(expf(-fabsf(x)))) * inv_tau);
+    } else {
+      a_s[i] = decay[head];
+    }
+  }
+  __syncthreads();
+  // Thread = (team member, column): member m of `teams` takes rows m, m + teams, ... of its column.
+  const int teams = max(1, (int)blockDim.x / dv);
+  float* S = S_state + ((size_t)state_slots[seq] * H + head) * DK * dv;
+  for (int item = threadIdx.x; item < teams * dv; item += blockDim.x) {
+    const int m = item / dv, j = item % dv;
+    const float v = to_f32(row[v_col + head * dv + j]);
+    float o = 0.f;
+#pragma unroll 8
+    for (int r = m; r < DK; r += teams) {
+      const float s = fmaf(k_s[r], v, a_s[r] * S[(size_t)r * dv + j]);
+      S[(size_t)r * dv + j] = s;
+      o = fmaf(s, q_s[r], o);
+    }
+    part_s[m * dv + j] = o;
+  }
+  __syncthreads();
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+    float o = 0.f;
+    for (int m = 0; m < teams; ++m) o += part_s[m * dv + j];
+    part_s[j] = o;  // row 0 of the partial sums becomes the head's output (only this thread reads column j)
+    ss += o * o;
+  }
+  const float r = 1.f / sqrtf(block_sum(ss, red) / (float)dv + eps);
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+    const float g = to_f32(row[gate_col + head * dv + j]);
+    const float sg = 1.f / (1.f + expf(-g));
+    out[t * H * dv + head * dv + j] = from_f32<T>(part_s[j] * r * (norm_w ? norm_w[j] : 1.f) * (silu_gate ? g * sg : sg));
+  }
+}
+
 }  // namespace
 
 extern "C" int omnia_state_dk(void) { return STATE_DK; }
@@ -364,5 +447,25 @@ extern "C" int omnia_state_heads_out(const float* o_raw, const void* gate_rows, 
   OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(state_heads_out_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream,
                                           o_raw, (const T*)gate_rows, gate_stride, norm_w, eps, H, dv, tokens, silu_gate,
                                           (T*)out)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// A step of single tokens (cu_seqlens[i + 1] - cu_seqlens[i] is 1, or 0 for a request that sits out):
+// the input step, the recurrence and the heads' norm and gate in one kernel. z float32 or null (then decay).
+extern "C" int omnia_state_step(const void* proj, int stride, int q_col, int k_col, int v_col, int gate_col, int H, int dv,
+                                const float* inv_freq, int rot, const int* positions, float q_scale, float k_scale,
+                                const float* z, int z_stride, const float* z_bias, float inv_tau, const float* decay,
+                                float* S_state, const int* cu_seqlens, const int* state_slots, int num_seqs,
+                                const float* norm_w, float eps, int silu_gate, void* out, int dtype, cudaStream_t stream) {
+  if (num_seqs == 0) return 0;
+  if (H < 1 || dv < 1 || rot < 0 || rot > STATE_DK || rot % 2 || (z == nullptr && decay == nullptr))
+    return (int)cudaErrorInvalidValue;
+  const int teams = STATE_STEP_THREADS / dv > 0 ? STATE_STEP_THREADS / dv : 1;
+  const size_t smem = sizeof(float) * (3 * STATE_DK + (size_t)teams * dv);
+  if (smem > 40 * 1024) return (int)cudaErrorInvalidValue;
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(state_step_kernel<T>, dim3(H, num_seqs), dim3(STATE_STEP_THREADS), smem, stream,
+                                          (const T*)proj, stride, q_col, k_col, v_col, gate_col, H, dv, inv_freq, rot, positions,
+                                          q_scale, k_scale, z, z_stride, z_bias, inv_tau, decay, S_state, cu_seqlens,
+                                          state_slots, norm_w, eps, silu_gate, (T*)out)));
   return OMNIA_LAUNCH_RESULT();
 }

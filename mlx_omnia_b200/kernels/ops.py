@@ -1388,11 +1388,23 @@ def state_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gate
         decay_logits = decay_logits.float()
     defines = {"STATE_DK": dk}
     width = heads * dv
+    rot = 0 if inv_freq is None else 2 * inv_freq.shape[0]
+    if step.decode_only and cols is None and 4 * (3 * dk + max(1024 // dv, 1) * dv) <= 40 * 1024:
+        # Single tokens: the input step, the recurrence and the heads' norm and gate in one kernel.
+        out = torch.empty(tokens, width, dtype=proj.dtype, device=proj.device)
+        fn = _function("state_recurrence", "omnia_state_step",
+                       [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_float,
+                        c_float, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                        c_float, c_int, c_void_p, c_int, c_void_p], defines)
+        _check(fn(_ptr(proj), stride, q_col, k_col, v_col, gate_col, heads, dv, _ptr(inv_freq), rot, _ptr(step.positions),
+                  q_scale, k_scale, _ptr(decay_logits), decay_logits.stride(0) if channel else 0, _ptr(decay_bias), 1.0 / tau,
+                  _ptr(decay), _ptr(S), _ptr(step.cu_seqlens), _ptr(step.state_slots), step.num_seqs, _ptr(norm_weight), eps,
+                  int(gate == "silu"), _ptr(out), _code(proj.dtype), _stream()), "state_step")
+        return out
     if cols is None:
         cols = state_columns(step.num_seqs, heads, dk, dv, sm_count(proj.device))
     row_floats = 2 * (-(-heads * dk // 4) * 4) + -(-width // 4) * 4 + (-(-heads * dk // 4) * 4 if channel else 0)
     rows = torch.empty(tokens, row_floats, dtype=torch.float32, device=proj.device)
-    rot = 0 if inv_freq is None else 2 * inv_freq.shape[0]
     fn = _function("state_recurrence", "omnia_state_inputs",
                    [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
                     c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p], defines)

@@ -64,10 +64,11 @@ class Batch:
 def test_state_attention_over_portions_and_slots(dtype, H, dk, dv, cols, rot, channel):
     """Two requests in portions of 1 to 37 tokens from state slots that others used before: the state
     carried in float32 gives the plain recurrence over the whole sequence, with a decay per head or per
-    token and key channel, rotated or not, a head's columns cut into runs or not (also a last short run)."""
+    token and key channel, rotated or not, a head's columns cut into runs or not (also a last short run);
+    then four steps of one token each (the kernel that does a decoding step in one launch)."""
     g = torch.Generator().manual_seed(dk * 3 + dv)
     dt = DTYPES[dtype]
-    Ta, Tb = 75, 41
+    Ta, Tb = 79, 45
     width = 2 * H * dk + 2 * H * dv
     decay = [0.5, 0.9, 0.97, 0.999, 1.0][:H]
     tau, q_scale, k_scale = 2.5, 0.7, dk ** -0.5
@@ -79,8 +80,8 @@ def test_state_attention_over_portions_and_slots(dtype, H, dk, dv, cols, rot, ch
     S = torch.full((5, H, dk, dv), 3.0, dtype=torch.float32, device=CUDA)
     S[[3, 1]] = 0.0
     got = {"a": [], "b": []}
-    cuts = {"a": [0, 37, 38, 40, 56, 75], "b": [0, 1, 18, 19, 20, 41]}
-    for i in range(5):
+    cuts = {"a": [0, 37, 38, 40, 56, 75, 76, 77, 78, 79], "b": [0, 1, 18, 19, 20, 41, 42, 43, 44, 45]}
+    for i in range(9):
         a0, a1, b0, b1 = cuts["a"][i], cuts["a"][i + 1], cuts["b"][i], cuts["b"][i + 1]
         step = Batch([a1 - a0, b1 - b0], [a0, b0], [3, 1])
         proj = torch.cat([rows["a"][a0:a1], rows["b"][b0:b1]]).to(CUDA)
@@ -89,7 +90,7 @@ def test_state_attention_over_portions_and_slots(dtype, H, dk, dv, cols, rot, ch
                                   decay=None if channel else torch.tensor(decay, device=CUDA), decay_logits=z,
                                   decay_bias=bias.to(CUDA) if channel else None, tau=tau, inv_freq=inv_freq,
                                   q_scale=q_scale, k_scale=k_scale, norm_weight=w.to(CUDA) if channel else None,
-                                  gate="silu" if channel else "sigmoid", cols=cols)
+                                  gate="silu" if channel else "sigmoid", cols=None if step.decode_only else cols)
         got["a"].append(out[: a1 - a0])
         got["b"].append(out[a1 - a0:])
     for r, T in (("a", Ta), ("b", Tb)):
